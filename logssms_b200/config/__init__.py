@@ -5,11 +5,12 @@ from .specs import (AttentionSpec, BlockSpec, DenseMLPSpec, GLASpec, GatedMLPSpe
 from .falcon_h1 import FalconH1Config
 from .dudurax import DuduraxConfig
 from .kuvazen import KuvazenConfig
+from .pupopel import PupopelConfig
 
 __all__ = [
     "ConfigError", "architecture_of", "load_model_config", "make_model_config", "read_config_json", "require",
     "AttentionSpec", "BlockSpec", "GatedMLPSpec", "Mamba2Spec", "MixerSlot", "ModelSpec", "NormSpec",
     "RopeSpec", "ScheduleEntry", "FalconH1Config", "DuduraxConfig", "DenseMLPSpec", "GLASpec", "LatentAttentionSpec",
     "PostNormBlockSpec", "RoutedMLPSpec", "KuvazenConfig", "ClampedGLUSpec", "MinGRUSpec", "PooledWindowAttentionSpec",
-    "StreamBlockSpec", "TokenSideSpec",
+    "StreamBlockSpec", "TokenSideSpec", "PupopelConfig",
 ]

@@ -34,6 +34,7 @@ class NormSpec:
     eps: float
     kind: str = "rmsnorm"
     param_name: str = "weight"     # checkpoint name of the weight relative to the norm's prefix ("" : the prefix itself)
+    offset: float = 0.0            # the norm multiplies by offset + stored weight (1.0: a weight stored around zero)
 
 
 @dataclass(frozen=True)
@@ -137,7 +138,10 @@ class RoutedMLPSpec:
 
     `score`: "softmax" over all router outputs, or "sigmoid" of each.  `expert`: "clamped" (g~ sigmoid(act_alpha g~)
     (u~ + 1) with gate and up clamped at `limit`) or "silu" (silu(g) u).  `weigh`: the chosen expert's weight multiplies
-    its "output" or its "input".  `correction`: whether the checkpoint holds a correction of the choice."""
+    its "output" or its "input".  `correction`: whether the checkpoint holds a correction of the choice.  `score` "softmax_chosen": the
+    router's outputs themselves are ranked and the chosen experts' weights are the softmax over the chosen outputs alone; with it
+    go `expert` "silu" weighted at the "output".  `router_bias`: the router's outputs get a stored bias.  `shared_size` > 0: one
+    more expert of that size (of the routed experts' form) runs for every token with weight 1."""
     hidden_size: int
     expert_size: int
     num_experts: int
@@ -152,6 +156,8 @@ class RoutedMLPSpec:
     expert: str = "clamped"
     weigh: str = "output"
     correction: bool = True
+    router_bias: bool = False
+    shared_size: int = 0
     kind: str = "routed_mlp"
 
 
@@ -164,6 +170,75 @@ class ClampedGLUSpec:
     limit: float
     act_alpha: float = 1.702
     kind: str = "clamped_glu"
+
+
+@dataclass(frozen=True)
+class GLUSpec:
+    """Dense gated feed-forward down(act(gate(x)) * up(x)), act "gelu_tanh" or "silu"."""
+    hidden_size: int
+    intermediate_size: int
+    activation: str = "gelu_tanh"
+    kind: str = "glu"
+
+
+@dataclass(frozen=True)
+class DeltaRuleSpec:
+    """Gated delta rule with a decay per key channel: q, k (`num_key_heads` heads of `key_dim`) and v (`num_heads` heads of
+    `value_dim`) pass a short causal convolution of `conv_kernel` taps and silu; q and k become unit vectors per head
+    (x / sqrt(|x|^2 + unit_eps), q also times key_dim^-1/2); per head S <- diag(g) S, u = b (v - S^T k), S <- S + k u^T,
+    o = S^T q with g = exp(-exp(A_log) softplus(low-rank projection + dt_bias)) per key channel and b = sigmoid(.) per
+    head; o is RMS-normed per head, times sigmoid of a low-rank gate, then the output projection."""
+    hidden_size: int
+    num_heads: int
+    num_key_heads: int
+    key_dim: int
+    value_dim: int
+    conv_kernel: int
+    norm_eps: float
+    unit_eps: float = 1e-6
+    kind: str = "channel_delta"
+
+
+@dataclass(frozen=True)
+class SinkAttentionSpec:
+    """Causal grouped-query attention without rotation: queries and keys RMS-normed per head (a weight each, shared by the
+    heads), the query times 1 + temp_coef * ln(floor((p + 1) / temp_every) + 1) at position p (temp_every 0: no such
+    factor); score = softmax_scale * (q . k) - slope_h * (i - j) with slope_h = 2^(-slope_span * (h + 1) / heads)
+    (slope_span 0: no bias); with `sink` a stored number per head joins the softmax's denominator as exp(sink_h)."""
+    hidden_size: int
+    num_heads: int
+    num_kv_heads: int
+    head_dim: int
+    value_dim: int
+    softmax_scale: float
+    norm_eps: float
+    temp_coef: float = 0.0
+    temp_every: int = 0
+    slope_span: float = 8.0
+    sink: bool = True
+    kind: str = "sink_attention"
+
+
+@dataclass(frozen=True)
+class LightningAttentionSpec:
+    """Linear attention with one fixed decay per head: q, k, v = silu(projection); S <- decay_h S + k v^T, o = S^T q; the
+    heads' outputs are RMS-normed together, times sigmoid(gate projection), then the output projection."""
+    hidden_size: int
+    num_heads: int
+    key_dim: int
+    value_dim: int
+    decay: tuple[float, ...]
+    norm_eps: float
+    kind: str = "lightning_attention"
+
+
+@dataclass(frozen=True)
+class MixerPairSpec:
+    """Two mixers side by side on the same input; the result is the sum of their outputs, each times its slot's
+    `out_scale`.  At most one of them keeps keys and values."""
+    left: Any          # MixerSlot
+    right: Any         # MixerSlot
+    kind: str = "mixer_pair"
 
 
 @dataclass(frozen=True)
@@ -269,6 +344,27 @@ class StreamBlockSpec:
 
 
 @dataclass(frozen=True)
+class ParallelStreamBlockSpec:
+    """Block on a 32-bit stream whose sublayers all read ONE norm's output: h = norm(x); x <- x + mixer(h) + feed_forward(h)
+    (a block without a feed-forward adds the mixer alone)."""
+    prefix: str
+    mixer: MixerSlot
+    norm: NormSpec
+    norm_name: str
+    feed_forward: Any                 # None: no feed-forward sublayer
+    feed_forward_name: str
+    kind: str = "parallel_stream"
+
+
+@dataclass(frozen=True)
+class StreamInputSpec:
+    """x <- W [x ; x0] on a 32-bit stream, x0 the rows the stream began as (the embedding's output); W [width, 2 * width]
+    is stored at the model's root under `name`."""
+    hidden_size: int
+    name: str
+
+
+@dataclass(frozen=True)
 class ScheduleEntry:
     """One execution of a layer.  `layer` indexes `ModelSpec.layers` (a layer
     may appear in several entries: its weights then run more than once).
@@ -278,6 +374,7 @@ class ScheduleEntry:
     layer: int
     cache: int
     writes_cache: bool = True
+    opens: int | None = None      # index into `ModelSpec.stream_inputs`: that input is applied right before this execution
 
 
 @dataclass(frozen=True)
@@ -296,6 +393,7 @@ class ModelSpec:
     embedding_kind: str = "embedding"       # registry.EMBEDDINGS: built as cls(vocab_size, hidden_size, multiplier)
     lm_head_kind: str = "lm_head"           # registry.HEADS: built as cls(vocab_size, hidden_size, multiplier, tied_to)
     embedding_options: tuple[tuple[str, Any], ...] = ()    # further keyword arguments of the embedding's constructor
+    stream_inputs: tuple[StreamInputSpec, ...] = ()         # see `ScheduleEntry.opens`
 
     def resolved_schedule(self) -> tuple[ScheduleEntry, ...]:
         if self.schedule:

@@ -11,7 +11,15 @@
 //   weighted sum of the values of query i is turned back by -i.  cos/sin come from tables [positions, n] (cos of
 //   the n/2 pairs, then sin) in float32.
 //
+//   Two options turn the same kernels into other attentions.  `pool` = 0: there are no blocks (with a window beyond
+//   every position: plain causal attention).  `slopes` (a number per query head): m_h * (i - j) is taken off the scaled
+//   score of token j.  `sinks` (a number per query head): exp(sink_h) joins the softmax's denominator, with no key and no
+//   value.  Without rotation tables (`v_rot` = 0) values are summed as they are cached.
+//
 //   pooled_prepare : per (token, head): rotate the query; rotate key and value and store them at the token's slot
+//   normed_prepare : per (token, head): RMS-norm the query and the key over the head's columns with a weight each
+//                    (shared by the heads), the query times 1 + coef * ln(floor((p + 1) / every) + 1) at position p;
+//                    store key and value at the token's slot
 //   pooled_blocks  : per token that ends a block: the means of the block's cached keys and values, stored at the
 //                    block's entry of a second paged cache (one entry per `pool` tokens)
 //   pooled_attention      : a warp per (token, head); a lane scores one key at a time, the lanes share the value
@@ -86,6 +94,63 @@ extern "C" int lb_pooled_prepare(const void* qkv, long row_stride, const int* po
     return launch_status();
 }
 
+// grid (tokens, Hq + 2 * Hkv); a warp per (token, head)
+template <typename T>
+__global__ void __launch_bounds__(32) normed_prepare_kernel(const T* __restrict__ qkv, long row_stride, const int* __restrict__ positions,
+                                                            const int* __restrict__ slot_mapping, const float* __restrict__ q_weight,
+                                                            const float* __restrict__ k_weight, float eps, float temp_coef, int temp_every,
+                                                            T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache,
+                                                            int Hq, int Hkv, int dim, int vdim, int write_kv) {
+    const size_t t = blockIdx.x;
+    int head = blockIdx.y;
+    const int lane = threadIdx.x;
+    const T* src;
+    T* dst;
+    const float* w;
+    float mult = 1.f;
+    int n;
+    if (head < Hq) {
+        src = qkv + t * row_stride + (size_t)head * dim;
+        dst = q_out + (t * Hq + head) * dim;
+        n = dim; w = q_weight;
+        if (temp_every > 0) mult = 1.f + temp_coef * logf((float)((max(positions[t], 0) + 1) / temp_every + 1));
+    } else {
+        if (!write_kv) return;
+        const long slot = slot_mapping[t];
+        if (slot < 0) return;
+        head -= Hq;
+        if (head < Hkv) {
+            src = qkv + t * row_stride + (size_t)Hq * dim + (size_t)head * dim;
+            dst = k_cache + ((size_t)slot * Hkv + head) * dim;
+            n = dim; w = k_weight;
+        } else {
+            head -= Hkv;
+            src = qkv + t * row_stride + (size_t)(Hq + Hkv) * dim + (size_t)head * vdim;
+            dst = v_cache + ((size_t)slot * Hkv + head) * vdim;
+            for (int c = lane; c < vdim; c += 32) dst[c] = src[c];
+            return;
+        }
+    }
+    float ss = 0.f;
+    for (int c = lane; c < n; c += 32) { const float v = to_f32(src[c]); ss += v * v; }
+    const float inv = mult / sqrtf(warp_sum(ss) / (float)n + eps);
+    for (int c = lane; c < n; c += 32) dst[c] = from_f32<T>(to_f32(src[c]) * inv * w[c]);
+}
+
+// qkv: [tokens, (Hq + Hkv) * dim + Hkv * vdim] (column view allowed); q_weight, k_weight: float32 [dim]; temp_every 0: no
+// query temperature
+extern "C" int lb_normed_prepare(const void* qkv, long row_stride, const int* positions, const int* slot_mapping, const float* q_weight,
+                                 const float* k_weight, float eps, float temp_coef, int temp_every, void* q_out, void* k_cache,
+                                 void* v_cache, int tokens, int Hq, int Hkv, int dim, int vdim, int write_kv, int dtype, void* stream) {
+    if (tokens <= 0) return kOk;
+    if (Hq <= 0 || Hkv <= 0 || dim <= 0 || vdim <= 0 || Hq + 2 * Hkv > 65535 || temp_every < 0) return kBadSize;
+    dim3 grid(tokens, Hq + 2 * Hkv);
+    LB_DISPATCH_DTYPE(dtype, normed_prepare_kernel<T><<<grid, 32, 0, (cudaStream_t)stream>>>(
+        (const T*)qkv, row_stride, positions, slot_mapping, q_weight, k_weight, eps, temp_coef, temp_every, (T*)q_out, (T*)k_cache,
+        (T*)v_cache, Hq, Hkv, dim, vdim, write_kv));
+    return launch_status();
+}
+
 // grid (tokens, Hkv): the token that ends a block writes the block's means
 template <typename T>
 __global__ void pooled_blocks_kernel(const T* __restrict__ k_cache, const T* __restrict__ v_cache, T* __restrict__ kp_cache,
@@ -139,6 +204,25 @@ __device__ __forceinline__ long key_row(int kk, int blocks, int first, const int
     return page < 0 ? -1 : (long)page * page_size + e % page_size;
 }
 
+// blocks that lie wholly behind the window of position i (none without pooling)
+__device__ __forceinline__ int blocks_behind(int i, int window, int pool) {
+    return pool > 0 ? max(0, (i - window + 1) / pool) : 0;
+}
+
+// what two options add to a softmax: a slope per head on the distance to a token, a sink per head in the denominator
+struct ScoreExtras {
+    const float* slopes;      // [Hq] or null
+    const float* sinks;       // [Hq] or null
+};
+
+// (maximum, sum, weighted values scaled by `f`) of a softmax once the sink has joined it
+__device__ __forceinline__ void join_sink(float sink, float& m, float& l, float& f) {
+    const float m_new = fmaxf(m, sink);
+    f = (m == -INFINITY) ? 0.f : expf(m - m_new);
+    l = l * f + expf(sink - m_new);
+    m = m_new;
+}
+
 // grid (tokens, ceil(Hq / kWarps)); dynamic shared memory: kWarps * dim floats (the scaled queries)
 template <typename T>
 __global__ void __launch_bounds__(kWarps * 32) pooled_attention_kernel(
@@ -146,7 +230,7 @@ __global__ void __launch_bounds__(kWarps * 32) pooled_attention_kernel(
         const T* __restrict__ vp_cache, const int* __restrict__ block_table, int table_width, const int* __restrict__ pooled_table,
         int pooled_width, const int* __restrict__ token_req, const int* __restrict__ positions, const int* __restrict__ token_list,
         const float* __restrict__ v_table, int v_rot, int table_rows, T* __restrict__ out, int Hq, int Hkv, int dim, int vdim,
-        int page_size, float scale, int window, int pool) {
+        int page_size, float scale, int window, int pool, ScoreExtras extras) {
     extern __shared__ float q_s[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int t = token_list != nullptr ? token_list[blockIdx.x] : blockIdx.x;
@@ -160,8 +244,9 @@ __global__ void __launch_bounds__(kWarps * 32) pooled_attention_kernel(
     const int* pages = block_table + (size_t)token_req[t] * table_width;
     const int* pooled_pages = pooled_table + (size_t)token_req[t] * pooled_width;
     const int first = max(0, pos - window + 1);
-    const int blocks = max(0, (pos - window + 1) / pool);
+    const int blocks = blocks_behind(pos, window, pool);
     const int keys = blocks + (pos - first + 1);
+    const float slope = extras.slopes != nullptr ? extras.slopes[head] : 0.f;
     float m = -INFINITY, l = 0.f, acc[kMaxValueRegs];
 #pragma unroll
     for (int r = 0; r < kMaxValueRegs; ++r) acc[r] = 0.f;
@@ -179,6 +264,7 @@ __global__ void __launch_bounds__(kWarps * 32) pooled_attention_kernel(
                 for (; c + 2 <= dim; c += 2) { a0 += qs[c] * to_f32(kr[c]); a1 += qs[c + 1] * to_f32(kr[c + 1]); }
                 if (c < dim) a0 += qs[c] * to_f32(kr[c]);
                 s = a0 + a1;
+                if (!pooled) s -= slope * (float)(pos - (first + kk - blocks));
             }
         }
         const float m_new = fmaxf(m, warp_max(s));
@@ -202,6 +288,12 @@ __global__ void __launch_bounds__(kWarps * 32) pooled_attention_kernel(
                 if (c < vdim) acc[r] += pj * to_f32(vr[c]);
             }
         }
+    }
+    if (extras.sinks != nullptr) {
+        float f;
+        join_sink(extras.sinks[head], m, l, f);
+#pragma unroll
+        for (int r = 0; r < kMaxValueRegs; ++r) acc[r] *= f;
     }
     // the summed values, turned back by the query's position (pairs of neighbouring columns: neighbouring lanes)
     const float inv_l = l > 0.f ? 1.f / l : 0.f;
@@ -227,9 +319,10 @@ extern "C" int lb_pooled_attention(const void* q, const void* k_cache, const voi
                                    const void* vp_cache, const int* block_table, int table_width, const int* pooled_table,
                                    int pooled_width, const int* token_req, const int* positions, const int* token_list,
                                    int num_tokens, const float* v_table, int v_rot, int table_rows, void* out, int Hq, int Hkv,
-                                   int dim, int vdim, int page_size, float scale, int window, int pool, int dtype, void* stream) {
+                                   int dim, int vdim, int page_size, float scale, int window, int pool, const float* slopes,
+                                   const float* sinks, int dtype, void* stream) {
     if (num_tokens <= 0) return kOk;
-    if (Hq <= 0 || Hkv <= 0 || Hq % Hkv || dim <= 0 || vdim <= 0 || page_size <= 0 || window <= 0 || pool <= 0 || (v_rot & 1)
+    if (Hq <= 0 || Hkv <= 0 || Hq % Hkv || dim <= 0 || vdim <= 0 || page_size <= 0 || window <= 0 || pool < 0 || (v_rot & 1)
         || v_rot > vdim || table_rows <= 0)
         return kBadSize;
     if (vdim > 32 * kMaxValueRegs || (size_t)kWarps * dim * sizeof(float) > 48 * 1024) return kTooLarge;
@@ -237,7 +330,7 @@ extern "C" int lb_pooled_attention(const void* q, const void* k_cache, const voi
     LB_DISPATCH_DTYPE(dtype, pooled_attention_kernel<T><<<grid, kWarps * 32, (size_t)kWarps * dim * sizeof(float), (cudaStream_t)stream>>>(
         (const T*)q, (const T*)k_cache, (const T*)v_cache, (const T*)kp_cache, (const T*)vp_cache, block_table, table_width,
         pooled_table, pooled_width, token_req, positions, token_list, v_table, v_rot, table_rows, (T*)out, Hq, Hkv, dim, vdim,
-        page_size, scale, window, pool));
+        page_size, scale, window, pool, ScoreExtras{slopes, sinks}));
     return launch_status();
 }
 
@@ -281,7 +374,8 @@ __global__ void __launch_bounds__(kSplitWarps * 32) pooled_attention_split_kerne
         const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache, const T* __restrict__ kp_cache,
         const T* __restrict__ vp_cache, const int* __restrict__ block_table, int table_width, const int* __restrict__ pooled_table,
         int pooled_width, const int* __restrict__ token_req, const int* __restrict__ positions, const int* __restrict__ token_list,
-        float* __restrict__ partial, int Hq, int Hkv, int dim, int vdim, int page_size, float scale, int window, int pool, int splits) {
+        float* __restrict__ partial, int Hq, int Hkv, int dim, int vdim, int page_size, float scale, int window, int pool, int splits,
+        ScoreExtras extras) {
     extern __shared__ __align__(16) float split_smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int slot = blockIdx.x;                                   // row of the scratch buffer
@@ -302,8 +396,11 @@ __global__ void __launch_bounds__(kSplitWarps * 32) pooled_attention_split_kerne
     const int* pages = block_table + (size_t)token_req[t] * table_width;
     const int* pooled_pages = pooled_table + (size_t)token_req[t] * pooled_width;
     const int first = max(0, pos - window + 1);
-    const int blocks = max(0, (pos - window + 1) / pool);
+    const int blocks = blocks_behind(pos, window, pool);
     const int keys = blocks + (pos - first + 1);
+    float slope[kPer];
+#pragma unroll
+    for (int h = 0; h < kPer; ++h) slope[h] = (extras.slopes != nullptr && h < nh) ? extras.slopes[h0 + h] : 0.f;
     const int chunk = ((keys + splits - 1) / splits + 31) / 32 * 32;
     const int k_begin = split * chunk, k_end = min(keys, k_begin + chunk);
     const bool vec = sizeof(T) == 2 && dim % 8 == 0;
@@ -326,6 +423,11 @@ __global__ void __launch_bounds__(kSplitWarps * 32) pooled_attention_split_kerne
             const T* kr = (pooled ? kp_cache : k_cache) + ((size_t)row * Hkv + g) * dim;
             if (vec) score_row_vec<kPer>(reinterpret_cast<const __nv_bfloat16*>(kr), qs, dim, s);
             else score_row<T, kPer>(kr, qs, dim, s);
+            if (!pooled) {
+                const float dist = (float)(pos - (first + kk - blocks));
+#pragma unroll
+                for (int h = 0; h < kPer; ++h) s[h] -= slope[h] * dist;
+            }
         }
         float p[kPer];
 #pragma unroll
@@ -389,7 +491,8 @@ __global__ void __launch_bounds__(kSplitWarps * 32) pooled_attention_split_kerne
 template <typename T>
 __global__ void __launch_bounds__(32) pooled_merge_kernel(const float* __restrict__ partial, const int* __restrict__ positions,
                                                           const int* __restrict__ token_list, const float* __restrict__ v_table, int v_rot,
-                                                          int table_rows, T* __restrict__ out, int Hq, int vdim, int splits) {
+                                                          int table_rows, T* __restrict__ out, int Hq, int vdim, int splits,
+                                                          const float* __restrict__ sinks) {
     const int lane = threadIdx.x, slot = blockIdx.x, head = blockIdx.y;
     const int t = token_list != nullptr ? token_list[slot] : slot;
     if (t < 0) return;
@@ -397,7 +500,8 @@ __global__ void __launch_bounds__(32) pooled_merge_kernel(const float* __restric
     const float* src0 = partial + ((size_t)slot * Hq + head) * splits * stride;
     float mm = -INFINITY;
     for (int s = 0; s < splits; ++s) mm = fmaxf(mm, src0[(size_t)s * stride]);
-    float ll = 0.f, o[kSplitValueRegs];
+    if (sinks != nullptr) mm = fmaxf(mm, sinks[head]);
+    float ll = sinks != nullptr ? expf(sinks[head] - mm) : 0.f, o[kSplitValueRegs];
 #pragma unroll
     for (int r = 0; r < kSplitValueRegs; ++r) o[r] = 0.f;
     for (int s = 0; s < splits; ++s) {
@@ -430,7 +534,7 @@ template <typename T, int kPer>
 static int launch_split(const void* q, const void* k_cache, const void* v_cache, const void* kp_cache, const void* vp_cache,
                         const int* block_table, int table_width, const int* pooled_table, int pooled_width, const int* token_req,
                         const int* positions, const int* token_list, int num_tokens, float* partial, int Hq, int Hkv, int dim, int vdim,
-                        int page_size, float scale, int window, int pool, int splits, void* stream) {
+                        int page_size, float scale, int window, int pool, int splits, ScoreExtras extras, void* stream) {
     const size_t smem = ((size_t)kPer * dim + (size_t)kSplitWarps * kPer * (vdim + 2)) * sizeof(float);
     static size_t have = 0;
     ensure_dynamic_smem(pooled_attention_split_kernel<T, kPer>, smem, have);
@@ -438,7 +542,8 @@ static int launch_split(const void* q, const void* k_cache, const void* v_cache,
     dim3 grid(num_tokens, Hkv * ((per + kPer - 1) / kPer), splits);
     pooled_attention_split_kernel<T, kPer><<<grid, kSplitWarps * 32, smem, (cudaStream_t)stream>>>(
         (const T*)q, (const T*)k_cache, (const T*)v_cache, (const T*)kp_cache, (const T*)vp_cache, block_table, table_width,
-        pooled_table, pooled_width, token_req, positions, token_list, partial, Hq, Hkv, dim, vdim, page_size, scale, window, pool, splits);
+        pooled_table, pooled_width, token_req, positions, token_list, partial, Hq, Hkv, dim, vdim, page_size, scale, window, pool, splits,
+        extras);
     return launch_status();
 }
 
@@ -448,22 +553,23 @@ extern "C" int lb_pooled_attention_split(const void* q, const void* k_cache, con
                                          int pooled_width, const int* token_req, const int* positions, const int* token_list,
                                          int num_tokens, const float* v_table, int v_rot, int table_rows, float* partial, void* out,
                                          int Hq, int Hkv, int dim, int vdim, int page_size, float scale, int window, int pool,
-                                         int splits, int dtype, void* stream) {
+                                         int splits, const float* slopes, const float* sinks, int dtype, void* stream) {
     if (num_tokens <= 0) return kOk;
-    if (Hq <= 0 || Hkv <= 0 || Hq % Hkv || dim <= 0 || dim % 4 || vdim <= 0 || page_size <= 0 || window <= 0 || pool <= 0 || (v_rot & 1)
+    if (Hq <= 0 || Hkv <= 0 || Hq % Hkv || dim <= 0 || dim % 4 || vdim <= 0 || page_size <= 0 || window <= 0 || pool < 0 || (v_rot & 1)
         || v_rot > vdim || table_rows <= 0 || splits <= 0 || splits > 65535 || Hq > 65535)
         return kBadSize;
     if (vdim > 32 * kSplitValueRegs || dim > 1024) return kTooLarge;
     const int per = Hq / Hkv;
     int code;
 #define LB_SPLIT(PER) LB_DISPATCH_DTYPE(dtype, code = (launch_split<T, PER>(q, k_cache, v_cache, kp_cache, vp_cache, block_table, table_width, \
-        pooled_table, pooled_width, token_req, positions, token_list, num_tokens, partial, Hq, Hkv, dim, vdim, page_size, scale, window, pool, splits, stream)))
+        pooled_table, pooled_width, token_req, positions, token_list, num_tokens, partial, Hq, Hkv, dim, vdim, page_size, scale, window, pool, splits, \
+        ScoreExtras{slopes, nullptr}, stream)))
     if (per == 1) { LB_SPLIT(1); } else if (per == 2) { LB_SPLIT(2); } else { LB_SPLIT(4); }
 #undef LB_SPLIT
     if (code != 0) return code;
     dim3 grid(num_tokens, Hq);
     LB_DISPATCH_DTYPE(dtype, pooled_merge_kernel<T><<<grid, 32, 0, (cudaStream_t)stream>>>(partial, positions, token_list, v_table, v_rot,
-                                                                                           table_rows, (T*)out, Hq, vdim, splits));
+                                                                                           table_rows, (T*)out, Hq, vdim, splits, sinks));
     return launch_status();
 }
 
@@ -494,7 +600,7 @@ __global__ void __launch_bounds__(kTileThreads) pooled_attention_tile_kernel(
         int table_width, const int* __restrict__ pooled_table, int pooled_width, const int* __restrict__ cu,
         const int* __restrict__ start_pos, const int* __restrict__ tiles, const float* __restrict__ v_table, int v_rot,
         int table_rows, __nv_bfloat16* __restrict__ out, int Hq, int Hkv, int dim, int vdim, int page_size, float scale,
-        int window, int pool, float* __restrict__ partial, int splits) {
+        int window, int pool, float* __restrict__ partial, int splits, ScoreExtras extras) {
     extern __shared__ __align__(16) unsigned char tile_smem[];
     const int b = tiles[2 * blockIdx.x];
     if (b < 0) return;
@@ -504,7 +610,8 @@ __global__ void __launch_bounds__(kTileThreads) pooled_attention_tile_kernel(
     const int row0 = cu[b] + t0, pos0 = start_pos[b] + t0;
     const int i_last = pos0 + n_q - 1;
     const int first = max(0, pos0 - window + 1);                    // the oldest token any query of the run sees
-    const int blocks = max(0, (i_last - window + 1) / pool);        // the blocks the last query sees
+    const int blocks = blocks_behind(i_last, window, pool);         // the blocks the last query sees
+    const float slope = extras.slopes != nullptr ? extras.slopes[head] : 0.f;
     const int keys = blocks + (i_last - first + 1);
     const int k_stride = dim + 8, v_stride = vdim + 8;              // elements; the pad staggers the banks
     // two buffers of a chunk's keys and values: the next chunk travels (cp.async) while this one is multiplied
@@ -537,10 +644,10 @@ __global__ void __launch_bounds__(kTileThreads) pooled_attention_tile_kernel(
             }
         }
     }
-    const int nb_lo = max(0, (i_lo - window + 1) / pool), nb_hi = max(0, (i_hi - window + 1) / pool);
+    const int nb_lo = blocks_behind(i_lo, window, pool), nb_hi = blocks_behind(i_hi, window, pool);
     // what the warp's 16 rows can see at all: a chunk wholly outside is skipped
     const int iw0 = pos0 + warp * 16, iw1 = min(iw0 + 15, i_last);
-    const int nb_warp = max(0, (iw1 - window + 1) / pool);
+    const int nb_warp = blocks_behind(iw1, window, pool);
     float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
     float o[kValueTiles][4];
 #pragma unroll
@@ -608,11 +715,12 @@ __global__ void __launch_bounds__(kTileThreads) pooled_attention_tile_kernel(
                 const bool hi = x >= 2;
                 const int i = hi ? i_hi : i_lo;
                 bool seen = kk < keys && (hi ? r_hi : r_lo) < n_q;
+                float bias = 0.f;
                 if (seen) {
                     if (kk < blocks) seen = kk < (hi ? nb_hi : nb_lo);
-                    else { const int j = first + kk - blocks; seen = j <= i && j > i - window; }
+                    else { const int j = first + kk - blocks; seen = j <= i && j > i - window; bias = slope * (float)(i - j); }
                 }
-                const float v = seen ? sc[n][x] * scale : -INFINITY;
+                const float v = seen ? sc[n][x] * scale - bias : -INFINITY;
                 sc[n][x] = v;
                 if (hi) mx_hi = fmaxf(mx_hi, v); else mx_lo = fmaxf(mx_lo, v);
             }
@@ -676,6 +784,13 @@ __global__ void __launch_bounds__(kTileThreads) pooled_attention_tile_kernel(
         }
         return;
     }
+    if (extras.sinks != nullptr) {
+        float f_lo, f_hi;
+        join_sink(extras.sinks[head], m_lo, l_lo, f_lo);
+        join_sink(extras.sinks[head], m_hi, l_hi, f_hi);
+#pragma unroll
+        for (int n = 0; n < kValueTiles; ++n) { o[n][0] *= f_lo; o[n][1] *= f_lo; o[n][2] *= f_hi; o[n][3] *= f_hi; }
+    }
     // weights' sums, the turn back by the query's position, the store
     const float inv_lo = l_lo > 0.f ? 1.f / l_lo : 0.f, inv_hi = l_hi > 0.f ? 1.f / l_hi : 0.f;
     const int half = v_rot >> 1;
@@ -703,7 +818,7 @@ static int launch_tile(const void* q, const void* k_cache, const void* v_cache, 
                        const int* block_table, int table_width, const int* pooled_table, int pooled_width, const int* cu,
                        const int* start_pos, const int* tiles, int num_tiles, const float* v_table, int v_rot, int table_rows,
                        void* out, int Hq, int Hkv, int dim, int vdim, int page_size, float scale, int window, int pool,
-                       float* partial, int splits, void* stream) {
+                       float* partial, int splits, ScoreExtras extras, void* stream) {
     const size_t smem = (size_t)2 * kTileK * ((dim + 8) + (vdim + 8)) * sizeof(__nv_bfloat16);
     static size_t have = 0;
     ensure_dynamic_smem(pooled_attention_tile_kernel<kDimSteps, kValueTiles>, smem, have);
@@ -711,7 +826,8 @@ static int launch_tile(const void* q, const void* k_cache, const void* v_cache, 
     pooled_attention_tile_kernel<kDimSteps, kValueTiles><<<grid, kTileThreads, smem, (cudaStream_t)stream>>>(
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, (const __nv_bfloat16*)kp_cache,
         (const __nv_bfloat16*)vp_cache, block_table, table_width, pooled_table, pooled_width, cu, start_pos, tiles, v_table, v_rot,
-        table_rows, (__nv_bfloat16*)out, Hq, Hkv, dim, vdim, page_size, scale, window, pool, splits > 1 ? partial : nullptr, splits);
+        table_rows, (__nv_bfloat16*)out, Hq, Hkv, dim, vdim, page_size, scale, window, pool, splits > 1 ? partial : nullptr, splits,
+        extras);
     return launch_status();
 }
 
@@ -725,15 +841,15 @@ static int tile_dispatch(const void* q, const void* k_cache, const void* v_cache
                                         int pooled_width, const int* cu, const int* start_pos, const int* tiles, int num_tiles,
                                         const float* v_table, int v_rot, int table_rows, void* out, int Hq, int Hkv, int dim,
                                         int vdim, int page_size, float scale, int window, int pool, float* partial, int splits,
-                                        void* stream) {
+                                        ScoreExtras extras, void* stream) {
     if (num_tiles <= 0) return kOk;
     if (Hq <= 0 || Hkv <= 0 || Hq % Hkv || Hq > 65535 || dim <= 0 || dim % 16 || vdim <= 0 || vdim % 8 || page_size <= 0 || window <= 0
-        || pool <= 0 || (v_rot & 1) || v_rot > vdim || table_rows <= 0)
+        || pool < 0 || (v_rot & 1) || v_rot > vdim || table_rows <= 0)
         return kBadSize;
     if (dim > 128 || vdim > 128 || splits < 1 || splits > 64 || (splits > 1 && partial == nullptr)) return kTooLarge;
 #define LB_TILE(DS, VT) return launch_tile<DS, VT>(q, k_cache, v_cache, kp_cache, vp_cache, block_table, table_width, pooled_table, \
         pooled_width, cu, start_pos, tiles, num_tiles, v_table, v_rot, table_rows, out, Hq, Hkv, dim, vdim, page_size, scale, window, pool, \
-        partial, splits, stream)
+        partial, splits, extras, stream)
     const int ds = dim / 16, vt = vdim / 8;
     if (ds <= 2) { if (vt <= 4) LB_TILE(2, 4); if (vt <= 8) LB_TILE(2, 8); if (vt <= 12) LB_TILE(2, 12); LB_TILE(2, 16); }
     if (ds <= 4) { if (vt <= 4) LB_TILE(4, 4); if (vt <= 8) LB_TILE(4, 8); if (vt <= 12) LB_TILE(4, 12); LB_TILE(4, 16); }
@@ -749,13 +865,14 @@ extern "C" int lb_pooled_attention_tile(const void* q, const void* k_cache, cons
                                         int pooled_width, const int* cu, const int* start_pos, const int* tiles, int num_tiles,
                                         const int* positions, int tokens, const float* v_table, int v_rot, int table_rows, void* out,
                                         int Hq, int Hkv, int dim, int vdim, int page_size, float scale, int window, int pool,
-                                        float* partial, int splits, void* stream) {
+                                        float* partial, int splits, const float* slopes, const float* sinks, void* stream) {
+    // (with several CTAs per run the sink joins in the merge, once)
     const int code = tile_dispatch(q, k_cache, v_cache, kp_cache, vp_cache, block_table, table_width, pooled_table, pooled_width, cu,
                                    start_pos, tiles, num_tiles, v_table, v_rot, table_rows, out, Hq, Hkv, dim, vdim, page_size, scale,
-                                   window, pool, partial, splits, stream);
+                                   window, pool, partial, splits, ScoreExtras{slopes, splits > 1 ? nullptr : sinks}, stream);
     if (code != 0 || splits <= 1 || num_tiles <= 0 || tokens <= 0) return code;
     dim3 grid(tokens, Hq);
     pooled_merge_kernel<__nv_bfloat16><<<grid, 32, 0, (cudaStream_t)stream>>>(partial, positions, nullptr, v_table, v_rot, table_rows,
-                                                                            (__nv_bfloat16*)out, Hq, vdim, splits);
+                                                                            (__nv_bfloat16*)out, Hq, vdim, splits, sinks);
     return launch_status();
 }

@@ -1,6 +1,7 @@
 // Gated linear attention with a decay per key channel, token by token.
 //
 //   a_t[d]  = sigmoid(z_t[d]) ^ (1 / tau)            (32-bit: log-sigmoid, division by tau, exponential)
+//             or, with `head_decay`, one fixed decay per head for all its key channels and tokens (z is not read)
 //   S_t     = diag(a_t) S_{t-1} + k_t v_t^T            (S: [key channels, value channels] per head, 32-bit)
 //   o_t     = S_t^T (q_t * q_scale)
 //
@@ -9,7 +10,8 @@
 //                  A CTA owns (request, head, a tile of value channels); a thread owns R state rows of one value
 //                  column, DS threads of a warp share a column.  q, k, the decays and v of 8 tokens at a time are
 //                  staged in shared memory, so the inner loop touches registers and shared memory only.
-//  gla_norm_gate : y = o / sqrt(mean_head(o^2) + eps) * w[c] * silu(g), o in 32-bit, w shared by the heads.
+//  gla_norm_gate : y = o / sqrt(mean_head(o^2) + eps) * w[c] * act(g), o in 32-bit, w shared by the heads; act is
+//                  silu or the sigmoid.  With one "head" of the full width it is the gated norm over all heads together.
 #include "lb200/common.cuh"
 using namespace lb200;
 
@@ -23,7 +25,8 @@ template <typename T, int R, int DS>
 __global__ void gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, long row_stride,
                                 const float* __restrict__ z, float* __restrict__ o, float* state,
                                 const int* __restrict__ cu, const int* __restrict__ start_pos, const int* __restrict__ slots,
-                                const int* __restrict__ request_list, int H, int dim, int vdim, float inv_tau, float q_scale) {
+                                const int* __restrict__ request_list, int H, int dim, int vdim, float inv_tau, float q_scale,
+                                const float* __restrict__ head_decay) {
     constexpr int DP = R * DS;                       // key channels, padded
     extern __shared__ float sm[];
     const int cols = blockDim.x / DS;
@@ -55,7 +58,7 @@ __global__ void gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k
                 const size_t row = (size_t)(t0 + tt);
                 qv = to_f32(q[row * row_stride + h * dim + d]) * q_scale;
                 kv = to_f32(k[row * row_stride + h * dim + d]);
-                av = expf(log_sigmoid(z[(row * H + h) * dim + d]) * inv_tau);
+                av = head_decay != nullptr ? head_decay[h] : expf(log_sigmoid(z[(row * H + h) * dim + d]) * inv_tau);
             }
             qs[i] = qv; ks[i] = kv; as[i] = av;
         }
@@ -90,7 +93,7 @@ __global__ void gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k
 template <typename T, int R, int DS>
 static int launch_gla_scan(const void* q, const void* k, const void* v, long row_stride, const float* z, float* o, float* state,
                            const int* cu, const int* start_pos, const int* slots, const int* request_list, int num_requests,
-                           int H, int dim, int vdim, float inv_tau, float q_scale, cudaStream_t stream) {
+                           int H, int dim, int vdim, float inv_tau, float q_scale, const float* head_decay, cudaStream_t stream) {
     // few requests: narrow tiles, so that more CTAs share the work
     const int want = (num_requests * H * ((vdim * DS + 127) / 128) < 148) ? 32 : 128;
     const int threads = min(want, (vdim * DS + 31) / 32 * 32);
@@ -100,7 +103,7 @@ static int launch_gla_scan(const void* q, const void* k, const void* v, long row
     static size_t have = 0;
     ensure_dynamic_smem(gla_scan_kernel<T, R, DS>, smem, have);
     gla_scan_kernel<T, R, DS><<<grid, threads, smem, stream>>>((const T*)q, (const T*)k, (const T*)v, row_stride, z, o, state, cu,
-                                                               start_pos, slots, request_list, H, dim, vdim, inv_tau, q_scale);
+                                                               start_pos, slots, request_list, H, dim, vdim, inv_tau, q_scale, head_decay);
     return launch_status();
 }
 
@@ -108,13 +111,13 @@ static int launch_gla_scan(const void* q, const void* k, const void* v, long row
 // elements); z: float32 [tokens, H*dim]; o: float32 [tokens, H*vdim]; state: float32 [slots, H, dim, vdim].
 extern "C" int lb_gla_scan(const void* q, const void* k, const void* v, long row_stride, const float* z, float* o, float* state,
                            const int* cu, const int* start_pos, const int* slots, const int* request_list, int num_requests,
-                           int H, int dim, int vdim, float tau, float q_scale, int dtype, void* stream) {
+                           int H, int dim, int vdim, float tau, float q_scale, const float* head_decay, int dtype, void* stream) {
     if (num_requests <= 0) return kOk;
     if (H <= 0 || dim <= 0 || vdim <= 0 || !(tau > 0.f)) return kBadSize;
     if (dim > 512) return kTooLarge;
     cudaStream_t st = (cudaStream_t)stream;
 #define LB_GLA(R_, DS_) LB_DISPATCH_DTYPE(dtype, return (launch_gla_scan<T, R_, DS_>(q, k, v, row_stride, z, o, state, cu, start_pos, \
-        slots, request_list, num_requests, H, dim, vdim, 1.f / tau, q_scale, st)))
+        slots, request_list, num_requests, H, dim, vdim, 1.f / tau, q_scale, head_decay, st)))
     if (dim <= 16) { LB_GLA(16, 1); }
     else if (dim <= 32) { LB_GLA(32, 1); }
     else if (dim <= 64) { LB_GLA(64, 1); }
@@ -128,7 +131,8 @@ extern "C" int lb_gla_scan(const void* q, const void* k, const void* v, long row
 // grid (rows, heads)
 template <typename T>
 __global__ void gla_norm_gate_kernel(const float* __restrict__ o, const T* __restrict__ gate, long gate_stride,
-                                     const float* __restrict__ weight, T* __restrict__ out, int H, int vdim, float eps) {
+                                     const float* __restrict__ weight, T* __restrict__ out, int H, int vdim, float eps,
+                                     int sigmoid_gate) {
     __shared__ float red[32];
     const size_t row = blockIdx.x;
     const int h = blockIdx.y;
@@ -139,18 +143,18 @@ __global__ void gla_norm_gate_kernel(const float* __restrict__ o, const T* __res
     const float inv = 1.f / sqrtf(ss / (float)vdim + eps);
     for (int c = threadIdx.x; c < vdim; c += blockDim.x) {
         const float g = to_f32(gate[row * gate_stride + h * vdim + c]);
-        out[(row * H + h) * vdim + c] = from_f32<T>(orow[c] * inv * weight[c] * silu_f(g));
+        out[(row * H + h) * vdim + c] = from_f32<T>(orow[c] * inv * weight[c] * (sigmoid_gate ? 1.f / (1.f + expf(-g)) : silu_f(g)));
     }
 }
 
 extern "C" int lb_gla_norm_gate(const float* o, const void* gate, long gate_stride, const float* weight, void* out, int rows,
-                                int H, int vdim, float eps, int dtype, void* stream) {
+                                int H, int vdim, float eps, int sigmoid_gate, int dtype, void* stream) {
     if (rows <= 0) return kOk;
-    if (H <= 0 || vdim <= 0) return kBadSize;
+    if (H <= 0 || vdim <= 0 || H > 65535) return kBadSize;
     const int threads = min(256, (vdim + 31) / 32 * 32);
     dim3 grid(rows, H);
     LB_DISPATCH_DTYPE(dtype, gla_norm_gate_kernel<T><<<grid, threads, 0, (cudaStream_t)stream>>>(
-        o, (const T*)gate, gate_stride, weight, (T*)out, H, vdim, eps));
+        o, (const T*)gate, gate_stride, weight, (T*)out, H, vdim, eps, sigmoid_gate));
     return launch_status();
 }
 
@@ -176,7 +180,7 @@ __global__ void __launch_bounds__(128) gla_chunk_prepare_kernel(
         const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k, long row_stride, const float* __restrict__ z,
         const int* __restrict__ cu, const int* __restrict__ chunks, __nv_bfloat16* __restrict__ q_in,
         __nv_bfloat16* __restrict__ k_end, float* __restrict__ A, float* __restrict__ D, int H, int dim, float inv_tau,
-        float q_scale) {
+        float q_scale, const float* __restrict__ head_decay) {
     extern __shared__ float sm[];
     float* b = sm;                         // [16][dim] log-decays, then their running sums
     float* qs = b + kChunk * dim;
@@ -191,7 +195,7 @@ __global__ void __launch_bounds__(128) gla_chunk_prepare_kernel(
         float ld = 0.f, qv = 0.f, kv = 0.f;
         if (j < n) {
             const size_t row = (size_t)(t0 + j);
-            ld = log_sigmoid(z[(row * H + h) * dim + d]) * inv_tau;
+            ld = head_decay != nullptr ? logf(head_decay[h]) : log_sigmoid(z[(row * H + h) * dim + d]) * inv_tau;
             qv = to_f32(q[row * row_stride + h * dim + d]) * q_scale;
             kv = to_f32(k[row * row_stride + h * dim + d]);
         }
@@ -444,7 +448,7 @@ extern "C" int lb_gla_chunked(const void* q, const void* k, const void* v, long 
                               const int* cu, const int* start_pos, const int* slots, const int* chunks, int num_chunks,
                               const int* per_request, int num_long, void* q_in, void* k_end, float* A, float* D, int H, int dim,
                               int vdim, float tau, float q_scale, const int* segments, int num_segments, float* seg_state,
-                              float* seg_decay, void* stream) {
+                              float* seg_decay, const float* head_decay, void* stream) {
     if (num_chunks <= 0 || num_long <= 0) return kOk;
     if (H <= 0 || dim <= 0 || vdim <= 0 || !(tau > 0.f) || dim % 16) return kBadSize;
     if (dim > 256) return kTooLarge;
@@ -455,7 +459,7 @@ extern "C" int lb_gla_chunked(const void* q, const void* k, const void* v, long 
         static size_t have = 0;
         ensure_dynamic_smem(gla_chunk_prepare_kernel, smem, have);
         gla_chunk_prepare_kernel<<<dim3(num_chunks, H), 128, smem, st>>>((const bf*)q, (const bf*)k, row_stride, z, cu, chunks,
-                                                                        (bf*)q_in, (bf*)k_end, A, D, H, dim, 1.f / tau, q_scale);
+                                                                        (bf*)q_in, (bf*)k_end, A, D, H, dim, 1.f / tau, q_scale, head_decay);
         const int rc = launch_status();
         if (rc != 0) return rc;
     }

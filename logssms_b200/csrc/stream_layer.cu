@@ -5,6 +5,8 @@
 //                     first divided by its root mean square, sqrt(mean(y^2) + unit_eps))
 //                     x_out = v (may be x itself), h = N(v) * w rounded to the activation dtype (what the next
 //                     sublayer's products read; N may be "none": h is v rounded)
+//   stream_add_many : v = x + sum_i s_i * y_i (up to four addends, a scalar each), x_out = v in place, h = N(v) * w
+//   stream_pair_rows: [x rounded | x0] side by side, the input of a product over the stream and the rows it began as
 //   side_gate       : a = gelu_tanh(z) * e for the products z [tokens, dim] of a side input's gate (see below), for
 //                     steps of many tokens, whose two small products go to the library
 //   stream_side     : v = x + s * y as above, then the token's side input
@@ -107,6 +109,69 @@ extern "C" int lb_stream_add_norm(const float* x, const void* y, const float* ls
         ensure_dynamic_smem(stream_add_norm_kernel<T>, smem, have);
         stream_add_norm_kernel<T><<<rows, threads, smem, (cudaStream_t)stream>>>(x, (const T*)y, ls, unit_eps, w, eps, x_out, (T*)h_out, H, kind);
     });
+    return launch_status();
+}
+
+// v = x + sum_i s_i * y_i for up to four addends with a scalar each (the sublayers of a block whose mixers and feed-forward all
+// read one norm's output), x_out = v in place, h = N(v) * w as in `stream_add_norm`
+struct Addends {
+    const void* y[4];
+    float s[4];
+    int n;
+};
+
+template <typename T>
+__global__ void stream_add_many_kernel(float* x, Addends a, const float* __restrict__ w, float eps, T* __restrict__ h_out, int H, int kind) {
+    extern __shared__ float row[];
+    __shared__ float red[32];
+    const size_t base = (size_t)blockIdx.x * H;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        float v = x[base + c];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+            if (i < a.n) v += a.s[i] * to_f32(((const T*)a.y[i])[base + c]);
+        row[c] = v;
+        x[base + c] = v;
+    }
+    if (h_out == nullptr) return;
+    __syncthreads();
+    float mean, inv;
+    row_stats(row, H, kind, eps, red, mean, inv);
+    for (int c = threadIdx.x; c < H; c += blockDim.x) h_out[base + c] = from_f32<T>((row[c] - mean) * inv * (w != nullptr ? w[c] : 1.f));
+}
+
+extern "C" int lb_stream_add_many(float* x, const void* y0, const void* y1, const void* y2, const void* y3, float s0, float s1, float s2,
+                                  float s3, int n, const float* w, float eps, void* h_out, int rows, int H, int kind, int dtype,
+                                  void* stream) {
+    if (rows <= 0) return kOk;
+    if (H <= 0 || (size_t)H * sizeof(float) > 160 * 1024 || kind < kLayerNorm || kind > kNoNorm || n < 0 || n > 4) return kBadSize;
+    const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+    const size_t smem = (size_t)H * sizeof(float);
+    const Addends a = {{y0, y1, y2, y3}, {s0, s1, s2, s3}, n};
+    LB_DISPATCH_DTYPE(dtype, {
+        static size_t have = 0;
+        ensure_dynamic_smem(stream_add_many_kernel<T>, smem, have);
+        stream_add_many_kernel<T><<<rows, threads, smem, (cudaStream_t)stream>>>(x, a, w, eps, (T*)h_out, H, kind);
+    });
+    return launch_status();
+}
+
+// out[t] = [x[t] rounded to the activation dtype | x0[t]]: the input of a product that mixes the stream with the rows it began as
+template <typename T>
+__global__ void stream_pair_rows_kernel(const float* __restrict__ x, const T* __restrict__ x0, T* __restrict__ out, int H, size_t total) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const size_t t = i / (2 * H);
+    const int c = (int)(i % (2 * H));
+    out[i] = c < H ? from_f32<T>(x[t * H + c]) : x0[t * H + (c - H)];
+}
+
+extern "C" int lb_stream_pair_rows(const float* x, const void* x0, void* out, int rows, int H, int dtype, void* stream) {
+    if (rows <= 0) return kOk;
+    if (H <= 0) return kBadSize;
+    const size_t total = (size_t)rows * 2 * H;
+    LB_DISPATCH_DTYPE(dtype, stream_pair_rows_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+        x, (const T*)x0, (T*)out, H, total));
     return launch_status();
 }
 

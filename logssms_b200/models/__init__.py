@@ -41,4 +41,8 @@ from ..config.kuvazen import ARCHITECTURE as _KUVAZEN, KuvazenConfig  # noqa: E4
 
 register_architecture(_KUVAZEN, KuvazenConfig)
 
+from ..config.pupopel import ARCHITECTURE as _PUPOPEL, PupopelConfig  # noqa: E402
+
+register_architecture(_PUPOPEL, PupopelConfig)
+
 __all__ = ["Architecture", "DecoderModel", "build_model", "register_architecture"]

@@ -29,10 +29,17 @@ class DecoderModel(Part):
         # parts that several layers share and whose tensors are stored at the model's root (a second embedding table that
         # every layer reads a slice of): a layer puts them into `shared["model_parts"]` under their checkpoint prefix
         self.model_parts = dict(shared.get("model_parts", {}))
+        # products over the stream and the embedding's output that open a run of layers (`ScheduleEntry.opens`)
+        from ..parts.block import StreamInput
+        self.stream_inputs = [StreamInput(s, perturb_init) for s in getattr(spec, "stream_inputs", ())]
+        for s, part in zip(getattr(spec, "stream_inputs", ()), self.stream_inputs):
+            self.model_parts[s.name] = part
         self.schedule = spec.resolved_schedule()
         for e in self.schedule:
             if not 0 <= e.layer < len(self.layers):
                 raise ValueError(f"schedule names layer {e.layer}, the model has {len(self.layers)}")
+            if e.opens is not None and not 0 <= e.opens < len(self.stream_inputs):
+                raise ValueError(f"schedule names stream input {e.opens}, the model has {len(self.stream_inputs)}")
         self.num_cache_layers = max(e.cache for e in self.schedule) + 1
         # an embedding with per-request state (`needs_context`) gets a cache layer of its own behind the blocks'
         self.embedding_cache_layer = None
@@ -102,6 +109,7 @@ class DecoderModel(Part):
             else:
                 x = self.embedding.forward(ctx.token_ids)
         residual = None
+        x0 = x.act if (self.stream_inputs and isinstance(x, K.StreamRows)) else None     # the embedding's output, kept for them
         tap = ctx.extras.get("layer_tap")          # debugging: called with (run index, the stream after that layer run)
         for i, e in enumerate(self.schedule):
             # a block may hand its output on already joined with the residual (`SummedRows`) where the norm that
@@ -115,6 +123,11 @@ class DecoderModel(Part):
                                                            "takes_scaled_rows", False)
             # ... or, on a 32-bit stream, already normed by that norm (the kernel that closes the block does it on the way)
             ctx.extras["next_input_norm"] = getattr(nxt, "input_norm", None)
+            # (not where a product over the stream comes between this block and the next)
+            ctx.extras["next_opens"] = i + 1 < len(self.schedule) and self.schedule[i + 1].opens is not None
+            if e.opens is not None:
+                with nvtx_range("stream input"):
+                    x = self.stream_inputs[e.opens].forward(x, x0)
             if PROFILER.nvtx:                      # named ranges per layer (and per part inside it) for a timeline
                 with nvtx_range(f"layer {e.layer}"):
                     x, residual = self.layers[e.layer].forward(x, residual, ctx, e.cache, e.writes_cache)
@@ -125,6 +138,7 @@ class DecoderModel(Part):
         ctx.extras.pop("next_norm_takes_summed", None)
         ctx.extras.pop("next_norm_takes_scaled", None)
         ctx.extras.pop("next_input_norm", None)
+        ctx.extras.pop("next_opens", None)
         return x, residual
 
     def logits(self, x: torch.Tensor, residual, rows: torch.Tensor) -> torch.Tensor:

@@ -1068,18 +1068,29 @@ def skip_rmsnorm(stream: StreamRows, y: torch.Tensor | None, skip: float, weight
 
 
 # --------------------------------------------------------------------------- gated linear attention
+def _gla_decay_checks(z, head_decay, T: int, H: int, dk: int) -> None:
+    if head_decay is None:
+        _need(z is not None and z.dtype == torch.float32 and z.shape == (T, H * dk) and z.is_contiguous(),
+              "z must be contiguous float32 [tokens, H*key_dim]")
+    else:
+        _need(z is None and head_decay.dtype == torch.float32 and head_decay.shape == (H,) and head_decay.is_contiguous(),
+              "a fixed decay per head is float32 [H] and comes without z")
+
+
 def gla_scan(qkv: torch.Tensor, z: torch.Tensor, state: torch.Tensor, cu_seqlens: torch.Tensor, start_pos: torch.Tensor,
              slots: torch.Tensor, num_requests: int, num_heads: int, key_dim: int, value_dim: int, tau: float,
-             q_scale: float, request_list: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+             q_scale: float, request_list: torch.Tensor | None = None, out: torch.Tensor | None = None,
+             head_decay: torch.Tensor | None = None) -> torch.Tensor:
     """Token-by-token recurrence S <- diag(sigmoid(z)^(1/tau)) S + k v^T, o = S^T (q * q_scale) per head over every
     request's tokens.  qkv: [tokens, >= 2*H*key_dim + H*value_dim] with columns q | k | v first (unit column stride);
     z: float32 [tokens, H*key_dim]; state: float32 [slots, H, key_dim, value_dim], updated in place.  Returns float32
-    [tokens, H*value_dim]."""
-    _cuda(qkv, z, state, cu_seqlens, start_pos, slots, request_list)
+    [tokens, H*value_dim].  With `head_decay` (float32 [H]) every key channel of head h decays by head_decay[h] at every
+    token, and z (then None) is not read."""
+    _cuda(qkv, z, state, cu_seqlens, start_pos, slots, request_list, head_decay)
     H, dk, dv = num_heads, key_dim, value_dim
     T = qkv.shape[0]
     _need(qkv.dim() == 2 and qkv.stride(1) == 1 and qkv.shape[1] >= H * (2 * dk + dv), "qkv must hold the columns q | k | v")
-    _need(z.dtype == torch.float32 and z.shape == (T, H * dk) and z.is_contiguous(), "z must be contiguous float32 [tokens, H*key_dim]")
+    _gla_decay_checks(z, head_decay, T, H, dk)
     _need(state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (H, dk, dv),
           "the state must be contiguous float32 [slots, H, key_dim, value_dim]")
     for t, name in ((cu_seqlens, "cu_seqlens"), (start_pos, "start_pos"), (slots, "slots")):
@@ -1092,9 +1103,9 @@ def gla_scan(qkv: torch.Tensor, z: torch.Tensor, state: torch.Tensor, cu_seqlens
     item, base = qkv.element_size(), qkv.data_ptr()
     stride = qkv.stride(0) if T > 1 else qkv.shape[1]
     f = _fn("gla", "lb_gla_scan", [c_void_p, c_void_p, c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                   c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p])
+                                   c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p, c_int, c_void_p])
     _check(f(base, base + H * dk * item, base + 2 * H * dk * item, stride, _ptr(z), _ptr(o), _ptr(state), _ptr(cu_seqlens),
-             _ptr(start_pos), _ptr(slots), _ptr(request_list), n, H, dk, dv, tau, q_scale, _code(qkv), _stream()),
+             _ptr(start_pos), _ptr(slots), _ptr(request_list), n, H, dk, dv, tau, q_scale, _ptr(head_decay), _code(qkv), _stream()),
            "gla_scan", f"(key_dim {dk}, value_dim {dv})")
     return o
 
@@ -1112,18 +1123,19 @@ def gla_chunked_ok(qkv: torch.Tensor, key_dim: int) -> bool:
 def gla_chunked(qkv: torch.Tensor, z: torch.Tensor, state: torch.Tensor, cu_seqlens: torch.Tensor, start_pos: torch.Tensor,
                 slots: torch.Tensor, chunks: torch.Tensor, num_chunks: int, per_request: torch.Tensor, num_long: int,
                 num_heads: int, key_dim: int, value_dim: int, tau: float, q_scale: float, out: torch.Tensor,
-                segments: torch.Tensor | None = None, segment_requests: torch.Tensor | None = None) -> torch.Tensor:
+                segments: torch.Tensor | None = None, segment_requests: torch.Tensor | None = None,
+                head_decay: torch.Tensor | None = None) -> torch.Tensor:
     """The recurrence of `gla_scan` over the long portions of a step in chunks of `GLA_CHUNK` tokens on the tensor cores
     (see `csrc/gla.cu`); the rows of the other requests in `out` (float32 [tokens, H*value_dim]) are left alone.
     `chunks`, `per_request`: the work lists of `StepContext.long_portion_chunks(GLA_CHUNK)`.  With `segments` and
     `segment_requests` (`StepContext.long_portion_segments`) every request's segments run side by side, twice, with a
     pass over their states between: for steps whose few long portions would leave most of the GPU idle."""
-    _cuda(qkv, z, state, cu_seqlens, start_pos, slots, chunks, per_request, out)
+    _cuda(qkv, z, state, cu_seqlens, start_pos, slots, chunks, per_request, out, head_decay)
     H, dk, dv = num_heads, key_dim, value_dim
     T = qkv.shape[0]
     _need(gla_chunked_ok(qkv, dk), "gla_chunked takes bfloat16 operands with key channels a multiple of 16 up to 256")
     _need(qkv.dim() == 2 and qkv.stride(1) == 1 and qkv.shape[1] >= H * (2 * dk + dv), "qkv must hold the columns q | k | v")
-    _need(z.dtype == torch.float32 and z.shape == (T, H * dk) and z.is_contiguous(), "z must be contiguous float32 [tokens, H*key_dim]")
+    _gla_decay_checks(z, head_decay, T, H, dk)
     _need(state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (H, dk, dv),
           "the state must be contiguous float32 [slots, H, key_dim, value_dim]")
     _need(out.dtype == torch.float32 and out.shape == (T, H * dv) and out.is_contiguous(), "out must be contiguous float32 [tokens, H*value_dim]")
@@ -1146,11 +1158,11 @@ def gla_chunked(qkv: torch.Tensor, z: torch.Tensor, state: torch.Tensor, cu_seql
     item, base = qkv.element_size(), qkv.data_ptr()
     f = _fn("gla", "lb_gla_chunked", [c_void_p, c_void_p, c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                       c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-                                      c_float, c_float, c_void_p, c_int, c_void_p, c_void_p, c_void_p])
+                                      c_float, c_float, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
     _check(f(base, base + H * dk * item, base + 2 * H * dk * item, qkv.stride(0) if T > 1 else qkv.shape[1], _ptr(z), _ptr(out),
              _ptr(state), _ptr(cu_seqlens), _ptr(start_pos), _ptr(slots), _ptr(chunks), num_chunks, _ptr(per_request), num_long,
              _ptr(q_in), _ptr(k_end), _ptr(A), _ptr(D), H, dk, dv, tau, q_scale, _ptr(segments), n_seg, _ptr(seg_state),
-             _ptr(seg_decay), _stream()), "gla_chunked", f"(key_dim {dk}, value_dim {dv})", launches=2 if segments is None else 4)
+             _ptr(seg_decay), _ptr(head_decay), _stream()), "gla_chunked", f"(key_dim {dk}, value_dim {dv})", launches=2 if segments is None else 4)
     return out
 
 
@@ -1163,9 +1175,11 @@ def gla_segmented_pays(num_tokens: int, num_long: int, num_heads: int, value_dim
     return num_tokens >= 2 * GLA_SEGMENT * GLA_CHUNK and num_long * num_heads * -(-value_dim // 32) < _SM_COUNT
 
 
-def gla_norm_gate(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, num_heads: int) -> torch.Tensor:
-    """RMSNorm of every head's float32 output with one weight [value_dim] for all heads, times silu(gate); the result
-    has the gate's dtype.  `gate` may be a column view of a wider matrix."""
+def gla_norm_gate(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, num_heads: int,
+                  sigmoid_gate: bool = False) -> torch.Tensor:
+    """RMSNorm of every head's float32 output with one weight [value_dim] for all heads, times silu(gate) (or, with
+    `sigmoid_gate`, sigmoid(gate)); the result has the gate's dtype.  `gate` may be a column view of a wider matrix.  With
+    `num_heads` 1 it is the gated norm over the whole row."""
     _cuda(o, gate, weight)
     rows, width = o.shape
     dv = width // num_heads
@@ -1173,9 +1187,9 @@ def gla_norm_gate(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps
     _need(gate.shape == o.shape and gate.stride(1) == 1, "gate must match o, unit column stride")
     _need(weight.dtype == torch.float32 and weight.shape == (dv,) and weight.is_contiguous(), "weight must be float32 [value_dim]")
     out = torch.empty((rows, width), dtype=gate.dtype, device=o.device)
-    f = _fn("gla", "lb_gla_norm_gate", [c_void_p, c_void_p, c_long, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p])
+    f = _fn("gla", "lb_gla_norm_gate", [c_void_p, c_void_p, c_long, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p])
     _check(f(_ptr(o), _ptr(gate), gate.stride(0) if rows > 1 else gate.shape[1], _ptr(weight), _ptr(out), rows, num_heads, dv,
-             eps, _code(gate), _stream()), "gla_norm_gate")
+             eps, int(sigmoid_gate), _code(gate), _stream()), "gla_norm_gate")
     return out
 
 
@@ -1346,11 +1360,15 @@ def latent_attention_wide(qa: torch.Tensor, q_rot: torch.Tensor, c_cache: torch.
 
 # --------------------------------------------------------------------------- routed feed-forward
 def moe_route(h: torch.Tensor, w_router: torch.Tensor, correction: torch.Tensor | None, num_experts: int, top: int, groups: int,
-              keep: int, scale: float, sigmoid_scores: bool = False):
+              keep: int, scale: float, sigmoid_scores: bool = False, bias: torch.Tensor | None = None, chosen_softmax: bool = False):
     """(dense weights float32 [T, n], chosen int32 [T, top], their weights float32 [T, top], identity weight float32 [T]):
     see `csrc/moe.cu`.  `w_router` float32 [n, width]; outputs num_experts .. n-1 are identity experts.  Scores are the
-    softmax over all outputs, or with `sigmoid_scores` the sigmoid of each; `correction` (may be None) moves the choice only."""
-    _cuda(h, w_router, correction)
+    softmax over all outputs, or with `sigmoid_scores` the sigmoid of each; `correction` (may be None) moves the choice only.
+    With `chosen_softmax` the logits themselves are ranked and the weights are the softmax over the chosen logits alone.
+    `bias` (float32 [n], may be None) is added to the logits."""
+    _cuda(h, w_router, correction, bias)
+    _need(bias is None or (bias.dtype == torch.float32 and bias.shape == (w_router.shape[0],) and bias.is_contiguous()), "router bias float32 [n]")
+    _need(not (chosen_softmax and (sigmoid_scores or correction is not None)), "the softmax over the chosen logits takes no other score")
     T, width = h.shape
     n = w_router.shape[0]
     _need(h.is_contiguous() and w_router.dtype == torch.float32 and w_router.is_contiguous() and w_router.shape[1] == width
@@ -1360,33 +1378,47 @@ def moe_route(h: torch.Tensor, w_router: torch.Tensor, correction: torch.Tensor 
     chosen = torch.empty((T, top), dtype=torch.int32, device=h.device)
     chosen_w = torch.empty((T, top), dtype=torch.float32, device=h.device)
     idw = torch.empty((T,), dtype=torch.float32, device=h.device)
-    f = _fn("moe", "lb_moe_route", [c_void_p] * 7 + [c_int] * 7 + [c_float, c_int, c_int, c_void_p])
+    f = _fn("moe", "lb_moe_route", [c_void_p] * 7 + [c_int] * 7 + [c_float, c_int, c_void_p, c_int, c_void_p])
     _check(f(_ptr(h), _ptr(w_router), _ptr(correction), _ptr(dense), _ptr(chosen), _ptr(chosen_w), _ptr(idw), T, width, n,
-             num_experts, top, groups, keep, scale, int(sigmoid_scores), _code(h), _stream()), "moe_route",
+             num_experts, top, groups, keep, scale, 2 if chosen_softmax else int(sigmoid_scores), _ptr(bias), _code(h), _stream()), "moe_route",
            f"({n} outputs, top {top}, {groups} groups)")
     return dense, chosen, chosen_w, idw
 
 
-EXPERT_MODES = {"clamped": 0, "silu_input": 1}
+EXPERT_MODES = {"clamped": 0, "silu_input": 1, "silu": 2, "gelu_tanh": 3}
 
 
 def moe_activation(gate_up: torch.Tensor, dense: torch.Tensor | None, num_experts: int, limit: float, act_alpha: float,
-                   mode: str = "clamped") -> torch.Tensor:
+                   mode: str = "clamped", out: torch.Tensor | None = None) -> torch.Tensor:
     """gate_up: [T, experts * 2 * ff] (per expert gate | up); returns [T, experts * ff] with every expert's gated
     activation and the token's weight for that expert (0 where the expert was not chosen).  Mode "clamped": weight *
     g~ sigmoid(act_alpha g~) (u~ + 1) with gate and up clamped at `limit`; "silu_input": silu(w g) * (w u), the expert on
-    an input that was multiplied by the weight.  `dense` None: every weight is 1 (a dense gated layer: one expert)."""
-    _cuda(gate_up, dense)
+    an input that was multiplied by the weight; "silu", "gelu_tanh": weight * act(g) * u.  `dense` None: every weight is 1 (a
+    dense gated layer: one expert).  `gate_up` and `out` ([T, experts * ff]) may be column views of wider matrices."""
+    _cuda(gate_up, dense, out)
     T = gate_up.shape[0]
     ff = gate_up.shape[1] // (2 * num_experts)
-    _need(gate_up.is_contiguous() and gate_up.shape[1] == 2 * num_experts * ff, "gate_up must be contiguous [T, experts*2*ff]")
+    _need(gate_up.dim() == 2 and gate_up.stride(1) == 1 and gate_up.shape[1] == 2 * num_experts * ff, "gate_up must be [T, experts*2*ff], unit column stride")
     _need(dense is None or (dense.dtype == torch.float32 and dense.is_contiguous() and dense.shape[0] == T and dense.shape[1] >= num_experts),
           "dense weights float32 [T, n]")
-    y = torch.empty((T, num_experts * ff), dtype=gate_up.dtype, device=gate_up.device)
-    f = _fn("moe", "lb_moe_activation", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_int, c_void_p])
+    y = out if out is not None else torch.empty((T, num_experts * ff), dtype=gate_up.dtype, device=gate_up.device)
+    _need(y.shape == (T, num_experts * ff) and y.dtype == gate_up.dtype and y.stride(1) == 1, "out must be [T, experts*ff] of gate_up's dtype")
+    f = _fn("moe", "lb_moe_activation", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_long, c_long,
+                                         c_int, c_void_p])
     _check(f(_ptr(gate_up), _ptr(dense), _ptr(y), T, num_experts, ff, 0 if dense is None else dense.shape[1], limit, act_alpha,
-             EXPERT_MODES[mode], _code(gate_up), _stream()), "moe_activation")
+             EXPERT_MODES[mode], gate_up.stride(0) if T > 1 else max(gate_up.stride(0), gate_up.shape[1]),
+             y.stride(0) if T > 1 else max(y.stride(0), y.shape[1]), _code(gate_up), _stream()), "moe_activation")
     return y
+
+
+def silu_columns(x: torch.Tensor, cols: int, scale: torch.Tensor | None = None) -> torch.Tensor:
+    """silu over the first `cols` columns of every row of x, in place; with `scale` (float32 [cols]) of x * scale."""
+    _cuda(x, scale)
+    _need(x.dim() == 2 and x.stride(1) == 1 and 0 <= cols <= x.shape[1], "silu_columns wants rows with unit column stride")
+    _need(scale is None or (scale.dtype == torch.float32 and scale.shape == (cols,) and scale.is_contiguous()), "scale must be float32 [cols]")
+    f = _fn("moe", "lb_silu_columns", [c_void_p, c_long, c_int, c_int, c_void_p, c_int, c_void_p])
+    _check(f(_ptr(x), x.stride(0) if x.shape[0] > 1 else x.shape[1], x.shape[0], cols, _ptr(scale), _code(x), _stream()), "silu_columns")
+    return x
 
 
 def moe_add_identity(out: torch.Tensor, h: torch.Tensor, id_weight: torch.Tensor) -> torch.Tensor:
@@ -1573,6 +1605,30 @@ def pooled_prepare(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_di
     return q
 
 
+def normed_prepare(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, value_dim: int, positions: torch.Tensor,
+                   slot_mapping: torch.Tensor, q_weight: torch.Tensor, k_weight: torch.Tensor, eps: float, temp_coef: float,
+                   temp_every: int, k_cache: torch.Tensor, v_cache: torch.Tensor, write_kv: bool = True) -> torch.Tensor:
+    """Queries [tokens, heads, head_dim], RMS-normed per head over the head's columns with `q_weight` [head_dim] and times
+    1 + temp_coef * ln(floor((position + 1) / temp_every) + 1) (`temp_every` 0: times 1); keys normed the same way with
+    `k_weight`, and the values as they are, go to the caches at the tokens' slots.  Norm and temperature are 32-bit."""
+    _cuda(qkv, positions, slot_mapping, q_weight, k_weight, k_cache, v_cache)
+    _i32(positions, "positions"); _i32(slot_mapping, "slot_mapping")
+    T = qkv.shape[0]
+    _need(qkv.dim() == 2 and qkv.stride(1) == 1 and qkv.shape[1] == (num_heads + num_kv_heads) * head_dim + num_kv_heads * value_dim,
+          "qkv must be [tokens, q | k | v] with unit column stride")
+    _need(k_cache.dtype == v_cache.dtype == qkv.dtype and k_cache.is_contiguous() and v_cache.is_contiguous()
+          and k_cache.shape[2:] == (num_kv_heads, head_dim) and v_cache.shape[2:] == (num_kv_heads, value_dim), "caches must be [pages, page, kv_heads, dim]")
+    for w in (q_weight, k_weight):
+        _need(w.dtype == torch.float32 and w.shape == (head_dim,) and w.is_contiguous(), "norm weights must be float32 [head_dim]")
+    q = torch.empty((T, num_heads, head_dim), dtype=qkv.dtype, device=qkv.device)
+    f = _fn("attention_pooled", "lb_normed_prepare", [c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_float, c_int,
+                                                      c_void_p, c_void_p, c_void_p] + [c_int] * 7 + [c_void_p])
+    _check(f(_ptr(qkv), qkv.stride(0) if T > 1 else qkv.shape[1], _ptr(positions), _ptr(slot_mapping), _ptr(q_weight), _ptr(k_weight), eps,
+             temp_coef, temp_every, _ptr(q), _ptr(k_cache), _ptr(v_cache), T, num_heads, num_kv_heads, head_dim, value_dim,
+             int(write_kv), _code(qkv), _stream()), "normed_prepare")
+    return q
+
+
 def pooled_blocks(k_cache: torch.Tensor, v_cache: torch.Tensor, kp_cache: torch.Tensor, vp_cache: torch.Tensor,
                   positions: torch.Tensor, token_req: torch.Tensor, block_table: torch.Tensor, pooled_slots: torch.Tensor,
                   pool: int) -> None:
@@ -1590,27 +1646,49 @@ def pooled_blocks(k_cache: torch.Tensor, v_cache: torch.Tensor, kp_cache: torch.
            "pooled_blocks")
 
 
+def _width(t: torch.Tensor | None) -> int:
+    return 0 if t is None else t.shape[1]
+
+
+def _rows(t: torch.Tensor | None) -> int:
+    return 1 if t is None else max(t.shape[0], 1)
+
+
+def _score_extras(num_heads: int, pool: int, pooled_table, slopes, sinks) -> None:
+    """Checks of the options that the pooled-attention kernels share.  `slopes[h] * (i - j)` is taken off the scaled score of
+    query i (head h) and token j; `exp(sinks[h])` joins the softmax's denominator with no key and no value."""
+    _need(pool >= 0 and (pool == 0 or pooled_table is not None), "pooled blocks need their caches and table (pool 0: none)")
+    for t, name in ((slopes, "slopes"), (sinks, "sinks")):
+        _need(t is None or (t.is_cuda and t.dtype == torch.float32 and t.shape == (num_heads,) and t.is_contiguous()),
+              f"{name} must be float32 [heads] on the device")
+
+
 def pooled_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, kp_cache: torch.Tensor, vp_cache: torch.Tensor,
                      block_table: torch.Tensor, pooled_table: torch.Tensor, token_req: torch.Tensor, positions: torch.Tensor,
                      v_table: torch.Tensor, scale: float, window: int, pool: int, token_list: torch.Tensor | None = None,
-                     out: torch.Tensor | None = None) -> torch.Tensor:
+                     out: torch.Tensor | None = None, slopes: torch.Tensor | None = None, sinks: torch.Tensor | None = None) -> torch.Tensor:
     """[tokens, heads * value_dim]: attention of every (listed) token over its window's tokens and the pooled blocks
-    behind it, a warp per (token, head), everything in float32; the summed values are turned back by the query's position."""
+    behind it, a warp per (token, head), everything in float32; the summed values are turned back by the query's position.
+    `pool` 0: no blocks (the pooled caches and their table may be None); `v_table` None: values are not rotated; `slopes`,
+    `sinks` (float32 per query head, may be None): see `_score_extras`."""
     _cuda(q, k_cache, v_cache, kp_cache, vp_cache, block_table, pooled_table, token_req, positions, v_table, token_list)
     for t, name in ((block_table, "block_table"), (pooled_table, "pooled_table"), (token_req, "token_req"), (positions, "positions")):
-        _i32(t, name)
+        if t is not None:
+            _i32(t, name)
     T, H, dim = q.shape
+    _score_extras(H, pool, pooled_table, slopes, sinks)
     G, vdim = v_cache.shape[2], v_cache.shape[3]
     _need(q.is_contiguous() and q.dtype == k_cache.dtype, "queries must be contiguous [tokens, heads, dim] in the cache's dtype")
     if out is None:
         out = torch.empty((T, H * vdim), dtype=q.dtype, device=q.device)
     n = T if token_list is None else token_list.numel()
     f = _fn("attention_pooled", "lb_pooled_attention", [c_void_p] * 6 + [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
-                                                        c_void_p, c_int, c_int, c_void_p] + [c_int] * 5 + [c_float, c_int, c_int, c_int, c_void_p])
+                                                        c_void_p, c_int, c_int, c_void_p] + [c_int] * 5
+            + [c_float, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p])
     _check(f(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(kp_cache), _ptr(vp_cache), _ptr(block_table), block_table.shape[1],
-             _ptr(pooled_table), pooled_table.shape[1], _ptr(token_req), _ptr(positions), _ptr(token_list), n, _ptr(v_table),
-             v_table.shape[1], max(v_table.shape[0], 1), _ptr(out), H, G, dim, vdim, k_cache.shape[1], scale, window, pool, _code(q),
-             _stream()), "pooled_attention", f"(dim {dim}, value dim {vdim})")
+             _ptr(pooled_table), _width(pooled_table), _ptr(token_req), _ptr(positions), _ptr(token_list), n, _ptr(v_table),
+             _width(v_table), _rows(v_table), _ptr(out), H, G, dim, vdim, k_cache.shape[1], scale, window, pool, _ptr(slopes),
+             _ptr(sinks), _code(q), _stream()), "pooled_attention", f"(dim {dim}, value dim {vdim})")
     return out
 
 
@@ -1642,7 +1720,8 @@ def pooled_tile_splits(num_tiles: int, num_heads: int) -> int:
 def pooled_attention_tile(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, kp_cache: torch.Tensor, vp_cache: torch.Tensor,
                           block_table: torch.Tensor, pooled_table: torch.Tensor, cu_seqlens: torch.Tensor, start_pos: torch.Tensor,
                           positions: torch.Tensor, tiles: torch.Tensor, v_table: torch.Tensor, scale: float, window: int, pool: int,
-                          out: torch.Tensor, splits: int = 1) -> torch.Tensor:
+                          out: torch.Tensor, splits: int = 1, slopes: torch.Tensor | None = None,
+                          sinks: torch.Tensor | None = None) -> torch.Tensor:
     """The same attention for the long portions' runs of `pooled_attention_tile_q()` tokens (work list of
     `StepContext.long_portion_tiles`) on the tensor cores; writes those tokens' rows of `out` [tokens, heads * value_dim].
     With `splits` > 1 that many CTAs share a run's keys and a merge follows, which also writes the rows that no run covers
@@ -1650,19 +1729,21 @@ def pooled_attention_tile(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch
     _cuda(q, k_cache, v_cache, kp_cache, vp_cache, block_table, pooled_table, cu_seqlens, start_pos, positions, tiles, v_table, out)
     for t, name in ((block_table, "block_table"), (pooled_table, "pooled_table"), (cu_seqlens, "cu_seqlens"), (start_pos, "start_pos"),
                     (tiles, "tiles"), (positions, "positions")):
-        _i32(t, name)
+        if t is not None:
+            _i32(t, name)
     T, H, dim = q.shape
+    _score_extras(H, pool, pooled_table, slopes, sinks)
     G, vdim = v_cache.shape[2], v_cache.shape[3]
     _need(q.is_contiguous() and q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
           and out.is_contiguous() and out.shape == (T, H * vdim), "the tensor-core form takes contiguous bfloat16 tensors")
     partial = torch.empty((T, H, splits, vdim + 2), dtype=torch.float32, device=q.device) if splits > 1 else None
     f = _fn("attention_pooled", "lb_pooled_attention_tile", [c_void_p] * 6 + [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                                              c_void_p, c_int, c_void_p, c_int, c_int, c_void_p] + [c_int] * 5
-            + [c_float, c_int, c_int, c_void_p, c_int, c_void_p])
+            + [c_float, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p])
     _check(f(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(kp_cache), _ptr(vp_cache), _ptr(block_table), block_table.shape[1],
-             _ptr(pooled_table), pooled_table.shape[1], _ptr(cu_seqlens), _ptr(start_pos), _ptr(tiles), tiles.shape[0], _ptr(positions), T,
-             _ptr(v_table), v_table.shape[1], max(v_table.shape[0], 1), _ptr(out), H, G, dim, vdim, k_cache.shape[1], scale, window, pool,
-             _ptr(partial), splits, _stream()),
+             _ptr(pooled_table), _width(pooled_table), _ptr(cu_seqlens), _ptr(start_pos), _ptr(tiles), tiles.shape[0], _ptr(positions), T,
+             _ptr(v_table), _width(v_table), _rows(v_table), _ptr(out), H, G, dim, vdim, k_cache.shape[1], scale, window, pool,
+             _ptr(partial), splits, _ptr(slopes), _ptr(sinks), _stream()),
            "pooled_attention_tile", f"(dim {dim}, value dim {vdim})", launches=2 if splits > 1 else 1)
     return out
 
@@ -1680,13 +1761,16 @@ def pooled_splits(num_tokens: int, num_kv_heads: int, keys: int) -> int:
 def pooled_attention_split(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, kp_cache: torch.Tensor, vp_cache: torch.Tensor,
                            block_table: torch.Tensor, pooled_table: torch.Tensor, token_req: torch.Tensor, positions: torch.Tensor,
                            v_table: torch.Tensor, scale: float, window: int, pool: int, splits: int,
-                           token_list: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+                           token_list: torch.Tensor | None = None, out: torch.Tensor | None = None,
+                           slopes: torch.Tensor | None = None, sinks: torch.Tensor | None = None) -> torch.Tensor:
     """The attention of `pooled_attention` with every token's keys cut into `splits` ranges that run side by side and all
     query heads of a key/value head in one CTA; a merge kernel joins the ranges (two launches)."""
     _cuda(q, k_cache, v_cache, kp_cache, vp_cache, block_table, pooled_table, token_req, positions, v_table, token_list)
     for t, name in ((block_table, "block_table"), (pooled_table, "pooled_table"), (token_req, "token_req"), (positions, "positions")):
-        _i32(t, name)
+        if t is not None:
+            _i32(t, name)
     T, H, dim = q.shape
+    _score_extras(H, pool, pooled_table, slopes, sinks)
     G, vdim = v_cache.shape[2], v_cache.shape[3]
     _need(q.is_contiguous() and q.dtype == k_cache.dtype, "queries must be contiguous [tokens, heads, dim] in the cache's dtype")
     if out is None:
@@ -1695,9 +1779,86 @@ def pooled_attention_split(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torc
     partial = torch.empty((n, H, splits, vdim + 2), dtype=torch.float32, device=q.device)
     f = _fn("attention_pooled", "lb_pooled_attention_split", [c_void_p] * 6 + [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                                               c_void_p, c_int, c_int, c_void_p, c_void_p] + [c_int] * 5
-            + [c_float, c_int, c_int, c_int, c_int, c_void_p])
+            + [c_float, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p])
     _check(f(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(kp_cache), _ptr(vp_cache), _ptr(block_table), block_table.shape[1],
-             _ptr(pooled_table), pooled_table.shape[1], _ptr(token_req), _ptr(positions), _ptr(token_list), n, _ptr(v_table),
-             v_table.shape[1], max(v_table.shape[0], 1), _ptr(partial), _ptr(out), H, G, dim, vdim, k_cache.shape[1], scale, window, pool,
-             splits, _code(q), _stream()), "pooled_attention_split", f"(dim {dim}, value dim {vdim}, {splits} ranges)", launches=2)
+             _ptr(pooled_table), _width(pooled_table), _ptr(token_req), _ptr(positions), _ptr(token_list), n, _ptr(v_table),
+             _width(v_table), _rows(v_table), _ptr(partial), _ptr(out), H, G, dim, vdim, k_cache.shape[1], scale, window, pool,
+             splits, _ptr(slopes), _ptr(sinks), _code(q), _stream()), "pooled_attention_split", f"(dim {dim}, value dim {vdim}, {splits} ranges)", launches=2)
+    return out
+
+
+# --------------------------------------------------------------------------- gated delta rule
+def delta_scan(qkv: torch.Tensor, z: torch.Tensor, dt_bias: torch.Tensor, A_log: torch.Tensor, beta: torch.Tensor, state: torch.Tensor,
+               cu_seqlens: torch.Tensor, start_pos: torch.Tensor, slots: torch.Tensor, num_requests: int, num_heads: int,
+               num_key_heads: int, key_dim: int, value_dim: int, q_scale: float, unit_eps: float,
+               request_list: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Token-by-token gated delta rule per head over every request's tokens (see `csrc/delta.cu`): queries and keys made unit
+    vectors (the query times `q_scale`), a decay exp(-exp(A_log) softplus(z + dt_bias)) per key channel, a write gated by
+    sigmoid(beta), read-out after the write.  qkv: [tokens, >= 2*Hk*key_dim + H*value_dim] with columns q | k | v first
+    (unit column stride; query/key head of value head h is h // (H / Hk)); z: float32 [tokens, H*key_dim]; dt_bias: float32
+    [H*key_dim]; A_log: float32 [H]; beta: [tokens, H] logits (float32 or qkv's dtype, a column view allowed); state: float32
+    [slots, H, key_dim, value_dim], updated in place.  Returns float32 [tokens, H*value_dim]."""
+    _cuda(qkv, z, dt_bias, A_log, beta, state, cu_seqlens, start_pos, slots, request_list)
+    H, Hk, dk, dv = num_heads, num_key_heads, key_dim, value_dim
+    T = qkv.shape[0]
+    _need(qkv.dim() == 2 and qkv.stride(1) == 1 and qkv.shape[1] >= 2 * Hk * dk + H * dv, "qkv must hold the columns q | k | v")
+    _need(z.dtype == torch.float32 and z.shape == (T, H * dk) and z.is_contiguous(), "z must be contiguous float32 [tokens, H*key_dim]")
+    _need(dt_bias.dtype == torch.float32 and dt_bias.numel() == H * dk and dt_bias.is_contiguous() and A_log.dtype == torch.float32
+          and A_log.shape == (H,) and A_log.is_contiguous(), "dt_bias float32 [H*key_dim], A_log float32 [H]")
+    _need(beta.dim() == 2 and beta.shape == (T, H) and beta.stride(1) == 1 and beta.dtype in (torch.float32, qkv.dtype),
+          "beta must be [tokens, H] in float32 or the activation dtype")
+    _need(state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (H, dk, dv),
+          "the state must be contiguous float32 [slots, H, key_dim, value_dim]")
+    for t, name in ((cu_seqlens, "cu_seqlens"), (start_pos, "start_pos"), (slots, "slots")):
+        _i32(t, name)
+    n = num_requests
+    if request_list is not None:
+        _i32(request_list, "request_list")
+        n = request_list.numel()
+    o = out if out is not None else torch.empty((T, H * dv), dtype=torch.float32, device=qkv.device)
+    item, base = qkv.element_size(), qkv.data_ptr()
+    stride = qkv.stride(0) if T > 1 else qkv.shape[1]
+    f = _fn("delta", "lb_delta_scan", [c_void_p, c_void_p, c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_int,
+                                       c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                       c_float, c_float, c_int, c_void_p])
+    _check(f(base, base + Hk * dk * item, base + 2 * Hk * dk * item, stride, _ptr(z), _ptr(dt_bias), _ptr(A_log), _ptr(beta),
+             beta.stride(0) if T > 1 else max(beta.stride(0), H), int(beta.dtype == torch.float32), _ptr(o), _ptr(state),
+             _ptr(cu_seqlens), _ptr(start_pos), _ptr(slots), _ptr(request_list), n, H, Hk, dk, dv, q_scale, unit_eps, _code(qkv),
+             _stream()), "delta_scan", f"(key_dim {dk}, value_dim {dv})")
+    return o
+
+
+# --------------------------------------------------------------------------- a 32-bit stream whose sublayers all read one norm
+def stream_add_many(x: torch.Tensor, addends, weight: torch.Tensor | None, eps: float, kind: str,
+                    act_dtype: torch.dtype) -> tuple[torch.Tensor, torch.Tensor | None]:
+    """x += sum of scale * y over `addends` (up to four pairs (y, scale), y activations of the stream's shape) in place on the
+    float32 stream, then norm(x) * weight rounded to `act_dtype` (None without a weight; kind "none": x rounded).
+    Returns (x, normed)."""
+    rows, H = x.shape
+    ys = [y for y, _ in addends]
+    _cuda(x, weight, *ys)
+    _need(x.dtype == torch.float32 and x.is_contiguous(), "the stream must be contiguous float32")
+    _need(len(addends) <= 4, "at most four addends join the stream in one kernel")
+    for y in ys:
+        _need(y.shape == x.shape and y.dtype == act_dtype and y.is_contiguous(), "an addend must match the stream's shape")
+    _need(weight is None or (weight.dtype == torch.float32 and weight.shape == (H,) and weight.is_contiguous()), "weight must be float32 [width]")
+    h = None if (weight is None and kind != "none") else torch.empty((rows, H), dtype=act_dtype, device=x.device)
+    if not addends and h is None:
+        return x, None
+    ptrs = [_ptr(y) for y in ys] + [None] * (4 - len(ys))
+    scales = [float(s) for _, s in addends] + [0.0] * (4 - len(ys))
+    f = _fn("stream_layer", "lb_stream_add_many", [c_void_p] * 5 + [c_float] * 4 + [c_int, c_void_p, c_float, c_void_p, c_int, c_int, c_int,
+                                                   c_int, c_void_p])
+    _check(f(_ptr(x), *ptrs, *scales, len(ys), _ptr(weight), eps, _ptr(h), rows, H, NORM_KINDS[kind], _DTYPE_CODE[act_dtype], _stream()),
+           "stream_add_many", f"(width {H})")
+    return x, h
+
+
+def stream_pair_rows(x: torch.Tensor, x0: torch.Tensor) -> torch.Tensor:
+    """[rows, 2 * width] in x0's dtype: the float32 stream x rounded, beside x0."""
+    _cuda(x, x0)
+    _need(x.dtype == torch.float32 and x.is_contiguous() and x0.is_contiguous() and x0.shape == x.shape, "stream and first rows must match")
+    out = torch.empty((x.shape[0], 2 * x.shape[1]), dtype=x0.dtype, device=x.device)
+    f = _fn("stream_layer", "lb_stream_pair_rows", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(x), _ptr(x0), _ptr(out), x.shape[0], x.shape[1], _code(x0), _stream()), "stream_pair_rows")
     return out

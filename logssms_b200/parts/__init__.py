@@ -10,11 +10,16 @@ from .latent_attention import LatentAttention
 from .moe import ClampedGLU, DenseMLP, RoutedMLP
 from .mingru import MinGRU
 from .pooled_attention import PooledWindowAttention
-from .embedding import BareLMHead, Embedding, LMHead, NormedEmbedding, PairEmbedding
-from .block import PostNormBlock, PreNormParallelBlock, PreNormStreamBlock, TokenSideInput
+from .delta import ChannelDelta
+from .lightning import LightningAttention
+from .sink_attention import MixerPair, SinkAttention
+from .moe import GLU
+from .embedding import BareLMHead, Embedding, LMHead, NormedEmbedding, PairEmbedding, StreamEmbedding
+from .block import ParallelStreamBlock, PostNormBlock, PreNormParallelBlock, PreNormStreamBlock, StreamInput, TokenSideInput
 
 __all__ = ["MATRIX", "TABLE", "VECTOR", "ParamSpec", "Part", "Runtime", "StepContext", "RMSNorm",
            "RotaryEmbedding", "inverse_frequencies", "Attention", "Mamba2", "GatedMLP", "Embedding", "LMHead",
            "PreNormParallelBlock", "PostNormBlock", "GatedLinearAttention", "LatentAttention", "DenseMLP", "RoutedMLP",
            "PairEmbedding", "BareLMHead", "LayerNorm", "MinGRU", "PooledWindowAttention", "ClampedGLU", "NormedEmbedding",
-           "PreNormStreamBlock", "TokenSideInput"]
+           "PreNormStreamBlock", "TokenSideInput", "ChannelDelta", "LightningAttention", "MixerPair", "SinkAttention", "GLU",
+           "StreamEmbedding", "ParallelStreamBlock", "StreamInput"]

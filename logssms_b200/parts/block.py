@@ -355,3 +355,105 @@ class PreNormStreamBlock(Part):
         if h is None:
             return K.StreamRows(stream, x.act[:0]), None
         return K.StreamRows(stream, h, normed_by=nxt), None
+
+
+class StreamInput(Part):
+    """x <- W [x ; x0] on a 32-bit stream: x0 are the rows the stream began as (the embedding's output, in the activation
+    dtype), W [width, 2 * width] is stored at the model's root.  The product reads the stream rounded to the activation
+    dtype beside x0 (one small kernel lays them side by side) and its sums are the new stream, unrounded."""
+    kernels = ("stream_layer", "linear_skinny", "gemm_tcgen05")
+
+    def __init__(self, spec, perturb_init: bool = False):
+        self.spec = spec
+        self.weight = None
+
+    def param_specs(self):
+        from .base import MATRIX, ParamSpec, normal_init
+        H = self.spec.hidden_size
+        return {"": ParamSpec((H, 2 * H), MATRIX, normal_init((2 * H) ** -0.5 * 1.4))}
+
+    def bind(self, t):
+        self.weight = t[""]
+
+    def forward(self, x, x0: torch.Tensor):
+        if not isinstance(x, K.StreamRows):
+            raise ValueError("a stream input mixes a 32-bit stream (`StreamRows`) with the rows it began as")
+        y = K.linear(K.stream_pair_rows(x.f32, x0), self.weight, out_f32=True)
+        return K.StreamRows(y, x0[:0])
+
+
+def _addends(y, scale: float = 1.0) -> list:
+    """What a sublayer handed back, as a list of (rows, scale): a mixer of several branches hands back such a list itself."""
+    if isinstance(y, list):
+        return [(t, s * scale) for t, s in y]
+    return [(y, scale)]
+
+
+@BLOCKS.register("parallel_stream")
+class ParallelStreamBlock(Part):
+    """Block on a 32-bit stream (`K.StreamRows`) whose sublayers all read ONE norm: h = norm(x); x <- x + mixer(h) + ff(h).
+    The sum and the norm are 32-bit; the sublayers read h in the activation dtype.  One kernel besides the sublayers' own:
+    all their outputs (a mixer of several branches hands back several, each with its scale) join the stream and the NEXT
+    block's norm reads the result in one (`K.stream_add_many`); the block's own norm runs alone only where the block
+    before could not do it (the first layer, and right behind a product over the stream)."""
+
+    def __init__(self, spec, perturb_init: bool = False, shared: dict | None = None):
+        self.spec = spec
+        m = spec.mixer
+        if m.in_scale != 1.0:
+            raise ValueError("parallel_stream blocks take a mixer without an input multiplier")
+        self.mixer = MIXERS.get(m.spec.kind)(m.spec, perturb_init=perturb_init, shared=shared)
+        self.norm = NORMS.get(spec.norm.kind)(spec.norm, perturb_init)
+        if not hasattr(self.norm, "norm_kind"):
+            raise ValueError("parallel_stream blocks need a norm with a form on a 32-bit stream (`norm_kind`)")
+        self.feed_forward = None
+        if spec.feed_forward is not None:
+            self.feed_forward = FEED_FORWARDS.get(spec.feed_forward.kind)(spec.feed_forward, perturb_init=perturb_init, shared=shared)
+
+    @property
+    def input_norm(self):
+        return self.norm
+
+    def children(self):
+        s = self.spec
+        kids = {s.norm_name: self.norm, s.mixer.name: self.mixer}
+        if self.feed_forward is not None:
+            kids[s.feed_forward_name] = self.feed_forward
+        return kids
+
+    def cache_needs(self):
+        return self.mixer.cache_needs()
+
+    def setup(self, rt) -> None:
+        self.mixer.setup(rt)
+        if self.feed_forward is not None:
+            self.feed_forward.setup(rt)
+
+    def forward(self, x, residual, ctx, cache_layer: int, writes_cache: bool = True):
+        if not isinstance(x, K.StreamRows) or residual is not None:
+            raise ValueError("a parallel_stream block takes a 32-bit stream (`StreamRows`), as its embedding or the block before leaves it")
+        act = x.act.dtype
+        stream = x.f32
+        if x.normed_by is self.norm:
+            h = x.act
+        else:
+            _, h = K.stream_add_many(stream, [], self.norm.weight, self.norm.eps, self.norm.norm_kind, act)
+        with nvtx_range(self.spec.mixer.spec.kind):
+            joins = _addends(self.mixer.forward(h, ctx, cache_layer, writes_cache), self.spec.mixer.out_scale)
+        if self.feed_forward is not None:
+            with nvtx_range(self.spec.feed_forward.kind):
+                joins += _addends(self.feed_forward.forward(h))
+        # all sublayers' outputs join the stream in the kernel that also makes the next block's normed input
+        nxt = ctx.extras.get("next_input_norm")
+        nxt = nxt if (hasattr(nxt, "norm_kind") and not ctx.extras.get("next_opens")) else None
+        h = None
+        while joins:
+            now, joins = joins[:4], joins[4:]
+            last = not joins
+            if last and nxt is not None:
+                _, h = K.stream_add_many(stream, now, nxt.weight, nxt.eps, nxt.norm_kind, act)
+            else:
+                K.stream_add_many(stream, now, None, 0.0, "rmsnorm", act)
+        if h is None:
+            return K.StreamRows(stream, x.act[:0]), None
+        return K.StreamRows(stream, h, normed_by=nxt), None

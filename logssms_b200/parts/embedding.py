@@ -64,6 +64,31 @@ class PairEmbedding(Part):
                             self.multiplier, self.buckets, self.mul_prev, self.mul_cur, self.bad_ids)
 
 
+@EMBEDDINGS.register("stream_embedding")
+class StreamEmbedding(Part):
+    """The token's row of the table as the first value of a 32-bit stream (`K.StreamRows`); the rows themselves, in the
+    activation dtype, stay at hand as the stream's `act` (a model whose layers mix them in again reads them there).
+    Tensor: `embed`."""
+    kernels = ("embed", "norm")
+
+    def __init__(self, vocab_size: int, hidden_size: int, multiplier: float = 1.0):
+        if multiplier != 1.0:
+            raise ValueError("a stream embedding has no multiplier")
+        self.vocab_size, self.hidden_size = vocab_size, hidden_size
+        self.weight = self.bad_ids = None
+
+    def param_specs(self):
+        return {"embed": ParamSpec((self.vocab_size, self.hidden_size), MATRIX, normal_init(1.0))}
+
+    def bind(self, t):
+        self.weight = t["embed"]
+        self.bad_ids = torch.zeros(1, dtype=torch.int32, device=self.weight.device)
+
+    def forward(self, ids: torch.Tensor):
+        rows = K.embed_gather(self.weight, ids, 1.0, self.bad_ids)
+        return K.StreamRows(K.scale(rows, 1.0, to_f32=True), rows)
+
+
 @EMBEDDINGS.register("normed_embedding")
 class NormedEmbedding(Part):
     """The token's row of the table, normed (the norm of `norm`, a `NormSpec`, with its own weight): the first value of a

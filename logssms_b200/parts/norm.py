@@ -5,7 +5,7 @@ import torch
 
 from ..ops import kernels as K
 from ..registry import NORMS
-from .base import VECTOR, ParamSpec, Part, ones_init
+from .base import VECTOR, ParamSpec, Part, normal_init, ones_init
 
 
 @NORMS.register("rmsnorm")
@@ -23,14 +23,19 @@ class RMSNorm(Part):
     def __init__(self, spec, perturb_init: bool = False):
         self.size, self.eps = spec.size, spec.eps
         self.param_name = getattr(spec, "param_name", "weight")
+        # `offset`: the norm multiplies by offset + the stored weight (1.0: a weight that is stored around zero); the sum is
+        # made once, in 32-bit, when the weight arrives
+        self.offset = float(getattr(spec, "offset", 0.0))
         self._jitter = 0.1 if perturb_init else 0.0
         self.weight: torch.Tensor | None = None
 
     def param_specs(self):
+        if self.offset != 0.0:
+            return {self.param_name: ParamSpec((self.size,), VECTOR, normal_init(self._jitter))}
         return {self.param_name: ParamSpec((self.size,), VECTOR, ones_init(self._jitter))}
 
     def bind(self, t):
-        self.weight = t[self.param_name]
+        self.weight = t[self.param_name] if self.offset == 0.0 else t[self.param_name] + self.offset
 
     def post(self, stream, y, skip_scale: float = 1.0, *, extra=None, row_scale=None):
         """Post-norm on a 32-bit stream: norm(skip_scale * stream + y [+ row_scale[t] * extra]) as `K.StreamRows`."""
