@@ -7,7 +7,8 @@ embedding's output.
 
 config.json is nested: `vocab`, `width`, `norm.eps`, `loop` (start, stop, times) and `layers`, a list whose entries give
 `type` (the mixer), `mixer` (its sizes and constants) and `mlp` (the feed-forward, or null).  Every size and constant is
-read from there.
+read from there; the ranks of the delta rule's two low-rank projections are the checkpoint's (the optional keys
+`decay_rank` and `gate_rank` of its `mixer` only tell the random-weights writer what to draw).
 """
 from __future__ import annotations
 
@@ -149,7 +150,8 @@ class PupopelConfig:
         for i, (kind, m, mlp) in enumerate(self.layers):
             if kind == "channel_delta":
                 mixer = DeltaRuleSpec(hidden_size=H, num_heads=int(m["heads"]), num_key_heads=int(m["kv_heads"]), key_dim=int(m["dim"]),
-                                      value_dim=int(m["vdim"]), conv_kernel=int(m["conv"]), norm_eps=eps, unit_eps=UNIT_EPS)
+                                      value_dim=int(m["vdim"]), conv_kernel=int(m["conv"]), norm_eps=eps, unit_eps=UNIT_EPS,
+                                      decay_rank=m.get("decay_rank"), gate_rank=m.get("gate_rank"))
                 slot = MixerSlot(mixer, "mix.")
             else:
                 L, R = m["left"], m["right"]

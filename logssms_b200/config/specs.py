@@ -196,6 +196,8 @@ class DeltaRuleSpec:
     conv_kernel: int
     norm_eps: float
     unit_eps: float = 1e-6
+    decay_rank: int | None = None      # None: whatever the checkpoint's low-rank decay projection has
+    gate_rank: int | None = None       # the same for the low-rank output gate
     kind: str = "channel_delta"
 
 

@@ -25,7 +25,7 @@ class ChannelDelta(Part):
     sigmoid(g2 (g1 h)), then the output projection.
 
     Per-request state: the convolution's last taps - 1 inputs per channel (activation dtype) and S [heads, key_dim,
-    value_dim] in float32.  The six input products are one (rows q | k | v | b | a1 | g1, merged at bind time); the unit
+    value_dim] in float32.  The six input products are one (rows q | k | v | a1 | g1 | b, merged at bind time); the unit
     vectors, decays, gates, the state and the head norm are 32-bit in every engine dtype (`K.delta_scan`).
     Tensors: q, q.conv, k, k.conv, v, v.conv, b, A_log, dt_bias, a1, a2, g1, g2, norm, o."""
     kernels = ("delta", "conv", "gla", "moe", "linear_skinny", "gemm_tcgen05")
@@ -38,7 +38,8 @@ class ChannelDelta(Part):
         self.spec = spec
         self._jitter = 0.1 if perturb_init else 0.0
         self.in_w = self.conv_w = self.a2_w = self.g2_w = self.o_w = self.norm_w = self.A_log = self.dt_bias = None
-        self.rank_a = self.rank_g = -1
+        self.rank_a = -1 if spec.decay_rank is None else spec.decay_rank
+        self.rank_g = -1 if spec.gate_rank is None else spec.gate_rank
 
     def param_specs(self):
         s = self.spec
@@ -65,7 +66,7 @@ class ChannelDelta(Part):
             if t[lo].shape[0] != t[hi].shape[1]:
                 raise ValueError(f"the two projections {lo}, {hi} disagree on their rank: {tuple(t[lo].shape)} and {tuple(t[hi].shape)}")
         self.rank_a, self.rank_g = t["a1"].shape[0], t["g1"].shape[0]
-        self.in_w = torch.cat([t["q"], t["k"], t["v"], t["b"], t["a1"], t["g1"]], 0).contiguous()
+        self.in_w = torch.cat([t["q"], t["k"], t["v"], t["a1"], t["g1"], t["b"]], 0).contiguous()
         self.conv_w = torch.cat([t["q.conv"], t["k.conv"], t["v.conv"]], 0).contiguous()
         self.a2_w, self.g2_w, self.o_w, self.norm_w = t["a2"].contiguous(), t["g2"].contiguous(), t["o"], t["norm"]
         self.A_log, self.dt_bias = t["A_log"], t["dt_bias"]
@@ -85,16 +86,17 @@ class ChannelDelta(Part):
         s = self.spec
         H, Hk, dk, dv = s.num_heads, s.num_key_heads, s.key_dim, s.value_dim
         C = 2 * Hk * dk + H * dv
-        proj = K.linear(x, self.in_w)                                     # q | k | v | write gate | low-rank decay, gate inputs
+        proj = K.linear(x, self.in_w)                                     # q | k | v | low-rank decay, gate inputs | write gate
         states = ctx.cache.states[cache_layer]
         if s.conv_kernel > 1:
             conv = K.causal_conv1d(proj[:, :C], self.conv_w, None, states["conv"], ctx.cu_seqlens, ctx.start_pos, ctx.slots,
                                    ctx.num_requests, ctx.max_len, (C, C), (1.0, 1.0, 1.0))
         else:
             conv = K.silu_columns(proj, C, scale=self.conv_w.view(-1))           # one tap: a scale per channel, nothing carried
-        beta = proj[:, C:C + H]
-        z = K.linear(proj[:, C + H:C + H + self.rank_a], self.a2_w, out_f32=True)
-        gate = K.linear(proj[:, C + H + self.rank_a:], self.g2_w)
+        ra, rg = self.rank_a, self.rank_g
+        z = K.linear(proj[:, C:C + ra], self.a2_w, out_f32=True)
+        gate = K.linear(proj[:, C + ra:C + ra + rg], self.g2_w)
+        beta = proj[:, C + ra + rg:]
         o = K.delta_scan(conv, z, self.dt_bias, self.A_log, beta, states["delta"], ctx.cu_seqlens, ctx.start_pos, ctx.slots,
                          ctx.num_requests, H, Hk, dk, dv, dk ** -0.5, s.unit_eps)
         y = K.gla_norm_gate(o, gate, self.norm_w, s.norm_eps, H, sigmoid_gate=True)

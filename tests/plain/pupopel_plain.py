@@ -137,8 +137,9 @@ def lightning(h, W, state, *, heads, dim, vdim, decay, eps):
 def pair_mixer(h, W, state, m, eps):
     sub = lambda p: {k[len(p):]: v for k, v in W.items() if k.startswith(p)}
     L, R = m["left"], m["right"]
+    temp = L.get("q_temp") or {"coef": 0.0, "every": 1}           # no query factor: times 1
     left = sink_attention(h, sub("left."), state, heads=L["heads"], kv_heads=L["kv_heads"], dim=L["dim"], vdim=L["vdim"],
-                          scale=L["scale"], temp_coef=L["q_temp"]["coef"], temp_every=L["q_temp"]["every"], eps=eps)
+                          scale=L["scale"], temp_coef=temp["coef"], temp_every=temp["every"], eps=eps)
     right = lightning(h, sub("right."), state, heads=R["heads"], dim=R["dim"], vdim=R["vdim"], decay=R["decay"], eps=eps)
     return m["left_scale"] * left + m["right_scale"] * right
 
