@@ -784,7 +784,36 @@ KUVAZEN_SIZES = {
     "w1024": (_kuvazen_config(1024, 4, 8, 2, 64, 128, 1024, 16, 2048, 8, 2, 1024, 2048, 64, 32768), DESIGN_SIZES["w1024"][0]),
     "w2048": (_kuvazen_config(2048, 4, 16, 4, 128, 128, 2048, 16, 4096, 16, 4, 1408, 8192, 64, 65536), DESIGN_SIZES["w2048"][0]),
 }
-DESIGNS = {"dudurax": (DESIGN_SIZES, "falcon_h1"), "kuvazen": (KUVAZEN_SIZES, "dudurax")}
+
+def _pupopel_config(width: int, layers: int, heads: int, kv_heads: int, key_dim: int, value_dim: int, experts: int, top: int,
+                    expert_ff: int, shared_ff: int, dense_ff: int, vocab: int) -> dict:
+    """Layer sizes that resemble a real model's: three gated-delta-rule layers to one pair of softmax attention (a bias by
+    distance, a sink) and lightning attention, routed feed-forwards with a shared expert and one dense one in front; the
+    first two layers are a loop of one pass (a pass opens with its product over the stream and the embedding's output)."""
+    delta = {"type": "channel_delta", "mixer": {"heads": heads, "kv_heads": heads, "dim": key_dim, "vdim": value_dim, "conv": 4,
+                                                "decay_rank": 16, "gate_rank": 16}}
+    pair = {"type": "parallel",
+            "mixer": {"left": {"heads": heads, "kv_heads": kv_heads, "dim": key_dim, "vdim": key_dim, "scale": key_dim ** -0.5,
+                               "q_temp": {"coef": 0.1, "every": 1024}},
+                      "right": {"heads": heads, "dim": key_dim, "vdim": value_dim,
+                                "decay": [1.0 - 2.0 ** (-5 - 5 * h / max(heads - 1, 1)) for h in range(heads)]},
+                      "left_scale": 1.0, "right_scale": 1.0}}
+    moe = {"kind": "moe", "expert": {"ff": expert_ff}, "router": {"experts": experts, "top": top}, "shared": {"ff": shared_ff}}
+    out = []
+    for i in range(layers):
+        out.append({**(pair if i % 4 == 3 else delta), "mlp": {"kind": "dense", "ff": dense_ff} if i == 0 else moe})
+    return {"architecture": "Pupopel", "layers": out, "loop": {"start": 0, "stop": min(2, layers), "times": 1}, "norm": {"eps": 1e-5},
+            "vocab": vocab, "width": width}
+
+
+# Pupopel beside Dudurax (the closest existing model: a 32-bit stream, three recurrent layers with a matrix state per head to
+# one attention layer, routed feed-forwards computed over all experts) at the same width, depth, vocabulary, head, expert and
+# dense sizes
+PUPOPEL_SIZES = {
+    "w1024": (_pupopel_config(1024, 4, 8, 2, 64, 128, 8, 2, 1024, 1024, 2048, 32768), DESIGN_SIZES["w1024"][0]),
+    "w2048": (_pupopel_config(2048, 4, 16, 4, 128, 128, 16, 4, 1408, 1408, 8192, 65536), DESIGN_SIZES["w2048"][0]),
+}
+DESIGNS = {"dudurax": (DESIGN_SIZES, "falcon_h1"), "kuvazen": (KUVAZEN_SIZES, "dudurax"), "pupopel": (PUPOPEL_SIZES, "dudurax")}
 
 
 def _design_point(cfg: dict, vocab: int, K: int, W: int, batch: int, context: int) -> dict:
@@ -857,7 +886,7 @@ def _design_point(cfg: dict, vocab: int, K: int, W: int, batch: int, context: in
 
 def run_design(args) -> dict:
     """`--design NAME`: that design at a few layer sizes beside the closest existing model at the same width and depth
-    (Dudurax beside Falcon-H1, Kuvazen beside Dudurax)."""
+    (Dudurax beside Falcon-H1, Kuvazen and Pupopel beside Dudurax)."""
     table, beside = DESIGNS[args.design]
     sizes = {}
     for name, (new, closest) in table.items():
@@ -918,7 +947,7 @@ def main() -> int:
     ap.add_argument("--reference-timeout", type=int, default=900, help="seconds the reference arm may take")
     ap.add_argument("--probe", choices=["decode", "prefill", "mixed"], default=None,
                     help="a short run of one kind of step for a profiler (see profiles/); prints no benchmark line")
-    ap.add_argument("--design", choices=["dudurax", "kuvazen"], default=None,
+    ap.add_argument("--design", choices=["dudurax", "kuvazen", "pupopel"], default=None,
                     help="prefill and decode of another design at a few layer sizes beside the closest existing model "
                          "(one JSON line of its own; the default workload is untouched)")
     args = ap.parse_args()

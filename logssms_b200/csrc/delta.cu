@@ -17,7 +17,18 @@
 //               A CTA owns (request, head, a tile of value columns); a thread owns R state rows of one column, DS
 //               threads of a warp share a column.  The unit vectors, decays, gates and <k^, q^> of kDeltaTokens tokens
 //               at a time are made in shared memory by the CTA's warps (a warp per token), so the inner loop touches
-//               registers and shared memory only.  Query/key head of value head h: h / (H / Hk).
+//               registers and shared memory only.  Query/key head of value head h: h / (H / Hk).  This is the kernel of
+//               steps whose requests bring a token or two each (decoding).
+//
+// Prompt portions: the recurrence is a chain of dependent steps per value column (decay, <S'[:, c], k^>, its reduction
+// over the column's threads, the gated difference, the rank-one write), about a hundred cycles a token however wide the
+// GPU is, so everything that is NOT on that chain leaves the loop:
+//  delta_prepare      : a CTA per token, all tokens side by side: q^ and k^ (32-bit, zero-padded to DP = 16 * DS key
+//                       channels), and per value head a row [g[0..DP) | b | <k^, q^> | 0 | 0].
+//  delta_scan_rows    : the same ownership as delta_scan with 16 state rows a thread; the prepared rows of the next
+//                       kDeltaTokens-or-so tokens arrive by cp.async in a second buffer while the current ones are used.
+//                       A thread's rows are interleaved in fours (row (r / 4) * 4 DS + 4 s + r % 4) so that the 128-bit
+//                       shared-memory reads of a warp fall on distinct banks.
 #include "lb200/common.cuh"
 using namespace lb200;
 
