@@ -23,12 +23,14 @@
 // Prompt portions: the recurrence is a chain of dependent steps per value column (decay, <S'[:, c], k^>, its reduction
 // over the column's threads, the gated difference, the rank-one write), about a hundred cycles a token however wide the
 // GPU is, so everything that is NOT on that chain leaves the loop:
-//  delta_prepare      : a CTA per token, all tokens side by side: q^ and k^ (32-bit, zero-padded to DP = 16 * DS key
-//                       channels), and per value head a row [g[0..DP) | b | <k^, q^> | 0 | 0].
-//  delta_scan_rows    : the same ownership as delta_scan with 16 state rows a thread; the prepared rows of the next
-//                       kDeltaTokens-or-so tokens arrive by cp.async in a second buffer while the current ones are used.
-//                       A thread's rows are interleaved in fours (row (r / 4) * 4 DS + 4 s + r % 4) so that the 128-bit
-//                       shared-memory reads of a warp fall on distinct banks.
+//  delta_prepare   : a warp per (token, value head), all of them side by side: the row
+//                    [q^ (DP) | k^ (DP) | g (DP) | b | <k^, q^> | 0 | 0] in 32-bit, DP = 16 * DS key channels (zeros past
+//                    `dim`), and the head's values in 32-bit.
+//  delta_scan_rows : the same ownership as delta_scan with 16 state rows a thread (DS threads of a warp share a column);
+//                    the prepared rows and values of the next kTok tokens arrive by cp.async in a second buffer while
+//                    the current ones are used.  A thread's rows are
+//                    interleaved in fours (row 4 DS j + 4 s + i, j, i = 0..3) so that the 128-bit shared-memory reads of
+//                    the DS threads of a column are one contiguous run.
 #include "lb200/common.cuh"
 using namespace lb200;
 
@@ -146,6 +148,193 @@ static int launch_delta_scan(const void* q, const void* k, const void* v, long r
                                                                      (const TB*)beta, beta_stride, o, state, cu, start_pos, slots,
                                                                      request_list, H, Hk, dim, vdim, q_scale, unit_eps);
     return launch_status();
+}
+
+// --------------------------------------------------------------------------- prompt portions
+constexpr int kRows = 16;                            // state rows a thread of delta_scan_rows owns
+
+__device__ __forceinline__ unsigned delta_smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void delta_cp16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(delta_smem_u32(dst)), "l"(src));
+}
+__device__ __forceinline__ void delta_cp4(void* dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(delta_smem_u32(dst)), "l"(src));
+}
+__device__ __forceinline__ void delta_cp_commit() { asm volatile("cp.async.commit_group;"); }
+template <int N> __device__ __forceinline__ void delta_cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N)); }
+
+// A warp per (token, value head).  prepared: [tokens, H, 3 DP + 4]; values: [tokens, H * vdim].
+template <typename T, typename TB>
+__global__ void delta_prepare_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, long row_stride,
+                                     const float* __restrict__ z, const float* __restrict__ dt_bias, const float* __restrict__ A_log,
+                                     const TB* __restrict__ beta, long beta_stride, float* __restrict__ prepared, float* __restrict__ values,
+                                     long pairs, int H, int Hk, int dim, int vdim, int DP, float q_scale, float unit_eps) {
+    const int lane = threadIdx.x & 31;
+    const long pair = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (pair >= pairs) return;
+    const long t = pair / H;
+    const int h = (int)(pair % H), hk = h / (H / Hk);
+    const T* qr = q + t * row_stride + (size_t)hk * dim;
+    const T* kr = k + t * row_stride + (size_t)hk * dim;
+    float qq = 0.f, kk = 0.f, qk = 0.f;
+    for (int d = lane; d < dim; d += 32) {
+        const float a = to_f32(qr[d]), e = to_f32(kr[d]);
+        qq += a * a; kk += e * e; qk += a * e;
+    }
+    qq = warp_sum(qq); kk = warp_sum(kk); qk = warp_sum(qk);
+    const float qn = q_scale / sqrtf(qq + unit_eps), kn = 1.f / sqrtf(kk + unit_eps), rate = expf(A_log[h]);
+    float* row = prepared + (size_t)pair * (3 * DP + 4);
+    const float* zr = z + ((size_t)t * H + h) * dim;
+    for (int d = lane; d < DP; d += 32) {
+        const bool in = d < dim;
+        row[d] = in ? to_f32(qr[d]) * qn : 0.f;
+        row[DP + d] = in ? to_f32(kr[d]) * kn : 0.f;
+        row[2 * DP + d] = in ? expf(-rate * softplus_f(zr[d] + dt_bias[h * dim + d])) : 0.f;
+    }
+    if (lane < 4) {
+        float x = 0.f;
+        if (lane == 0) x = 1.f / (1.f + expf(-to_f32(beta[t * beta_stride + h])));
+        if (lane == 1) x = qk * qn * kn;
+        row[3 * DP + lane] = x;
+    }
+    const T* vr = v + t * row_stride + (size_t)h * vdim;
+    float* orow = values + ((size_t)t * H + h) * vdim;
+    for (int c = lane; c < vdim; c += 32) orow[c] = to_f32(vr[c]);
+}
+
+// A CTA owns (request, head, blockDim.x / DS value columns).
+template <int DS, int TOK>
+__global__ void __launch_bounds__(128) delta_scan_rows_kernel(const float* __restrict__ prepared, const float* __restrict__ values,
+                                                              float* __restrict__ o, float* state,
+                                                              const int* __restrict__ cu, const int* __restrict__ start_pos,
+                                                              const int* __restrict__ slots, const int* __restrict__ request_list,
+                                                              int H, int dim, int vdim) {
+    constexpr int DP = kRows * DS, ROW = 3 * DP + 4, PIECES = ROW / 4;
+    extern __shared__ __align__(16) float sm[];
+    const int cols = blockDim.x / DS;
+    float* rows = sm;                                // [2][TOK][ROW]
+    float* vals = sm + 2 * TOK * ROW;                // [2][TOK][cols]
+    const int b = request_list ? request_list[blockIdx.z] : blockIdx.z;
+    if (b < 0) return;
+    const int h = blockIdx.y;
+    const int col_local = threadIdx.x / DS, s = threadIdx.x % DS;
+    const int c = blockIdx.x * cols + col_local;
+    const int first = cu[b], last = cu[b + 1];
+    if (first >= last) return;
+    const size_t sbase = ((size_t)slots[b] * H + h) * dim * vdim;
+    const bool fresh = start_pos[b] == 0;
+    float S[kRows];
+#pragma unroll
+    for (int r = 0; r < kRows; ++r) {
+        const int d = (r >> 2) * 4 * DS + 4 * s + (r & 3);
+        S[r] = (!fresh && d < dim && c < vdim) ? state[sbase + (size_t)d * vdim + c] : 0.f;
+    }
+    auto fetch = [&](int t0, int buf) {
+        const int n = min(TOK, last - t0);
+        float* dst = rows + buf * TOK * ROW;
+        for (int i = threadIdx.x; i < n * PIECES; i += blockDim.x) {
+            const int tt = i / PIECES, piece = i % PIECES;
+            delta_cp16(dst + tt * ROW + piece * 4, prepared + ((size_t)(t0 + tt) * H + h) * ROW + piece * 4);
+        }
+        float* vd = vals + buf * TOK * cols;
+        for (int i = threadIdx.x; i < n * cols; i += blockDim.x) {
+            const int tt = i / cols, cc = blockIdx.x * cols + i % cols;
+            if (cc < vdim) delta_cp4(vd + i, values + ((size_t)(t0 + tt) * H + h) * vdim + cc);
+        }
+        delta_cp_commit();
+    };
+    fetch(first, 0);
+    int buf = 0;
+    for (int t0 = first; t0 < last; t0 += TOK, buf ^= 1) {
+        if (t0 + TOK < last) { fetch(t0 + TOK, buf ^ 1); delta_cp_wait<1>(); } else { delta_cp_wait<0>(); }
+        __syncthreads();
+        const int n = min(TOK, last - t0);
+        const float* base = rows + buf * TOK * ROW;
+        const float* vd = vals + buf * TOK * cols + col_local;
+        for (int tt = 0; tt < n; ++tt) {
+            const float4* qr = reinterpret_cast<const float4*>(base + tt * ROW) + s;
+            const float4* kr = qr + DP / 4;
+            const float4* gr = kr + DP / 4;
+            float4 kv[4];
+            float a[4], e[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float4 g = gr[j * DS], q4 = qr[j * DS];
+                kv[j] = kr[j * DS];
+                S[4 * j] *= g.x; S[4 * j + 1] *= g.y; S[4 * j + 2] *= g.z; S[4 * j + 3] *= g.w;
+                a[j] = kv[j].x * S[4 * j] + kv[j].y * S[4 * j + 1] + kv[j].z * S[4 * j + 2] + kv[j].w * S[4 * j + 3];
+                e[j] = q4.x * S[4 * j] + q4.y * S[4 * j + 1] + q4.z * S[4 * j + 2] + q4.w * S[4 * j + 3];
+            }
+            float dot_k = (a[0] + a[1]) + (a[2] + a[3]), dot_q = (e[0] + e[1]) + (e[2] + e[3]);
+#pragma unroll
+            for (int off = 1; off < DS; off <<= 1) {
+                dot_k += __shfl_xor_sync(0xffffffffu, dot_k, off);
+                dot_q += __shfl_xor_sync(0xffffffffu, dot_q, off);
+            }
+            const float2 gate = *reinterpret_cast<const float2*>(base + tt * ROW + 3 * DP);      // b, <k^, q^>
+            const float u = gate.x * (vd[tt * cols] - dot_k);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                S[4 * j] += kv[j].x * u; S[4 * j + 1] += kv[j].y * u; S[4 * j + 2] += kv[j].z * u; S[4 * j + 3] += kv[j].w * u;
+            }
+            if (s == 0 && c < vdim) o[((size_t)(t0 + tt) * H + h) * vdim + c] = dot_q + u * gate.y;
+        }
+        __syncthreads();                             // the buffer is fetched into again in the next round
+    }
+#pragma unroll
+    for (int r = 0; r < kRows; ++r) {
+        const int d = (r >> 2) * 4 * DS + 4 * s + (r & 3);
+        if (d < dim && c < vdim) state[sbase + (size_t)d * vdim + c] = S[r];
+    }
+}
+
+template <int DS, int TOK>
+static int launch_delta_scan_rows(const float* prepared, const float* values, float* o, float* state, const int* cu, const int* start_pos, const int* slots,
+                                  const int* request_list, int num_requests, int H, int dim, int vdim, cudaStream_t stream) {
+    const int threads = min(128, (vdim * DS + 31) / 32 * 32);
+    const int cols = threads / DS;
+    dim3 grid((vdim + cols - 1) / cols, H, num_requests);
+    const size_t smem = (size_t)2 * TOK * (3 * kRows * DS + 4 + cols) * sizeof(float);
+    static size_t have = 0;
+    ensure_dynamic_smem(delta_scan_rows_kernel<DS, TOK>, smem, have);
+    delta_scan_rows_kernel<DS, TOK><<<grid, threads, smem, stream>>>(prepared, values, o, state, cu, start_pos, slots, request_list, H, dim, vdim);
+    return launch_status();
+}
+
+// The long portions of a step: the requests of `request_list` (all, if null).  Operands as in lb_delta_scan, plus
+// prepared: float32 [tokens, H, 3 DP + 4] (DP: 16 times the power of two that reaches dim) and values: float32
+// [tokens, H*vdim], both scratch.  Every token of the step is prepared, the listed requests are scanned.
+extern "C" int lb_delta_scan_rows(const void* q, const void* k, const void* v, long row_stride, const float* z, const float* dt_bias,
+                                  const float* A_log, const void* beta, long beta_stride, int beta_f32, float* prepared, float* values, float* o,
+                                  float* state, const int* cu, const int* start_pos, const int* slots, const int* request_list,
+                                  int num_requests, long tokens, int H, int Hk, int dim, int vdim, float q_scale, float unit_eps,
+                                  int dtype, void* stream) {
+    if (num_requests <= 0 || tokens <= 0) return kOk;
+    if (H <= 0 || Hk <= 0 || H % Hk || dim <= 0 || vdim <= 0 || H > 65535 || num_requests > 65535) return kBadSize;
+    if (dim > 512) return kTooLarge;
+    cudaStream_t st = (cudaStream_t)stream;
+    int DS = 1;
+    while (kRows * DS < dim) DS <<= 1;
+    const long pairs = tokens * H;
+    const int warps = 4;
+    const unsigned blocks = (unsigned)((pairs + warps - 1) / warps);
+#define LB_PREPARE(TB_) delta_prepare_kernel<T, TB_><<<blocks, warps * 32, 0, st>>>((const T*)q, (const T*)k, (const T*)v, row_stride, z, \
+        dt_bias, A_log, (const TB_*)beta, beta_stride, prepared, values, pairs, H, Hk, dim, vdim, kRows * DS, q_scale, unit_eps)
+    LB_DISPATCH_DTYPE(dtype, { if (beta_f32) LB_PREPARE(float); else LB_PREPARE(T); });
+#undef LB_PREPARE
+    const int status = launch_status();
+    if (status != kOk) return status;
+#define LB_ROWS(DS_, TOK_) return launch_delta_scan_rows<DS_, TOK_>(prepared, values, o, state, cu, start_pos, slots, request_list, num_requests, \
+        H, dim, vdim, st)
+    switch (DS) {
+        case 1: LB_ROWS(1, 16);
+        case 2: LB_ROWS(2, 16);
+        case 4: LB_ROWS(4, 16);
+        case 8: LB_ROWS(8, 16);
+        case 16: LB_ROWS(16, 8);
+        default: LB_ROWS(32, 8);
+    }
+#undef LB_ROWS
 }
 
 // q, k: [tokens, Hk*dim] and v: [tokens, H*vdim], column views of one buffer (common row stride, in elements);

@@ -80,10 +80,10 @@ def test_delta_rule_in_portions(dtype, heads, kv_heads, dim, vdim, conv):
 
 
 @pytest.mark.parametrize("heads, kv_heads, dim, vdim, conv", [(4, 2, 64, 32, 4), (2, 2, 16, 40, 2), (3, 1, 128, 128, 4), (2, 2, 48, 24, 3),
-                                                              (1, 1, 256, 16, 4)])
+                                                              (1, 1, 256, 16, 4), (1, 1, 300, 6, 2), (2, 1, 17, 3, 3)])
 def test_delta_rule_of_long_portions_carries_the_state_from_chunk_to_chunk_and_step_to_step(heads, kv_heads, dim, vdim, conv):
-    """Portions of hundreds of tokens (both dtypes; a bfloat16 engine runs them in chunks) beside a short request and single
-    tokens, cut inside chunks."""
+    """Portions of hundreds of tokens (the kernel of long portions, whose rows arrive sixteen or eight tokens at a time)
+    beside a short request and single tokens (the token-by-token kernel), cut inside those blocks."""
     for dtype in DTYPES:
         part, stored, kw = delta_part(dtype, heads, kv_heads, dim, vdim, conv, seed=dim)
         cache, planner = cache_for([part.cache_needs()], dtype, max_requests=3, max_seq_len=1024)
