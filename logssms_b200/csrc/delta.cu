@@ -26,11 +26,11 @@
 //  delta_prepare   : a warp per (token, value head), all of them side by side: the row
 //                    [q^ (DP) | k^ (DP) | g (DP) | b | <k^, q^> | 0 | 0] in 32-bit, DP = 16 * DS key channels (zeros past
 //                    `dim`), and the head's values in 32-bit.
-//  delta_scan_rows : the same ownership as delta_scan with 16 state rows a thread (DS threads of a warp share a column);
-//                    the prepared rows and values of the next kTok tokens arrive by cp.async in a second buffer while
-//                    the current ones are used.  A thread's rows are
-//                    interleaved in fours (row 4 DS j + 4 s + i, j, i = 0..3) so that the 128-bit shared-memory reads of
-//                    the DS threads of a column are one contiguous run.
+//  delta_scan_rows : the same ownership as delta_scan with 4 to 16 state rows a thread (by the key channels; DS threads of
+//                    a warp share a column); the prepared rows and values of the next kTok tokens arrive by cp.async
+//                    in a second buffer while the current ones are used.  A thread's rows are interleaved in fours
+//                    (row 4 DS j + 4 s + i, i = 0..3) so that the 128-bit shared-memory reads of the DS threads of a
+//                    column are one contiguous run.
 #include "lb200/common.cuh"
 using namespace lb200;
 
@@ -151,7 +151,7 @@ static int launch_delta_scan(const void* q, const void* k, const void* v, long r
 }
 
 // --------------------------------------------------------------------------- prompt portions
-constexpr int kRows = 16;                            // state rows a thread of delta_scan_rows owns
+constexpr int kMinPadded = 16;                       // key channels are padded to a power of two, this at least
 
 __device__ __forceinline__ unsigned delta_smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void delta_cp16(void* dst, const void* src) {
@@ -203,13 +203,13 @@ __global__ void delta_prepare_kernel(const T* __restrict__ q, const T* __restric
 }
 
 // A CTA owns (request, head, blockDim.x / DS value columns).
-template <int DS, int TOK>
+template <int R, int DS, int TOK>
 __global__ void __launch_bounds__(128) delta_scan_rows_kernel(const float* __restrict__ prepared, const float* __restrict__ values,
                                                               float* __restrict__ o, float* state,
                                                               const int* __restrict__ cu, const int* __restrict__ start_pos,
                                                               const int* __restrict__ slots, const int* __restrict__ request_list,
                                                               int H, int dim, int vdim) {
-    constexpr int DP = kRows * DS, ROW = 3 * DP + 4, PIECES = ROW / 4;
+    constexpr int DP = R * DS, ROW = 3 * DP + 4, PIECES = ROW / 4, Q = R / 4;
     extern __shared__ __align__(16) float sm[];
     const int cols = blockDim.x / DS;
     float* rows = sm;                                // [2][TOK][ROW]
@@ -223,9 +223,9 @@ __global__ void __launch_bounds__(128) delta_scan_rows_kernel(const float* __res
     if (first >= last) return;
     const size_t sbase = ((size_t)slots[b] * H + h) * dim * vdim;
     const bool fresh = start_pos[b] == 0;
-    float S[kRows];
+    float S[R];
 #pragma unroll
-    for (int r = 0; r < kRows; ++r) {
+    for (int r = 0; r < R; ++r) {
         const int d = (r >> 2) * 4 * DS + 4 * s + (r & 3);
         S[r] = (!fresh && d < dim && c < vdim) ? state[sbase + (size_t)d * vdim + c] : 0.f;
     }
@@ -255,17 +255,20 @@ __global__ void __launch_bounds__(128) delta_scan_rows_kernel(const float* __res
             const float4* qr = reinterpret_cast<const float4*>(base + tt * ROW) + s;
             const float4* kr = qr + DP / 4;
             const float4* gr = kr + DP / 4;
-            float4 kv[4];
-            float a[4], e[4];
+            float4 kv[Q];
+            float a[Q], e[Q];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
+            for (int j = 0; j < Q; ++j) {
                 const float4 g = gr[j * DS], q4 = qr[j * DS];
                 kv[j] = kr[j * DS];
                 S[4 * j] *= g.x; S[4 * j + 1] *= g.y; S[4 * j + 2] *= g.z; S[4 * j + 3] *= g.w;
                 a[j] = kv[j].x * S[4 * j] + kv[j].y * S[4 * j + 1] + kv[j].z * S[4 * j + 2] + kv[j].w * S[4 * j + 3];
                 e[j] = q4.x * S[4 * j] + q4.y * S[4 * j + 1] + q4.z * S[4 * j + 2] + q4.w * S[4 * j + 3];
             }
-            float dot_k = (a[0] + a[1]) + (a[2] + a[3]), dot_q = (e[0] + e[1]) + (e[2] + e[3]);
+            float dot_k, dot_q;
+            if constexpr (Q == 4) { dot_k = (a[0] + a[1]) + (a[2] + a[3]); dot_q = (e[0] + e[1]) + (e[2] + e[3]); }
+            else if constexpr (Q == 2) { dot_k = a[0] + a[1]; dot_q = e[0] + e[1]; }
+            else { dot_k = a[0]; dot_q = e[0]; }
 #pragma unroll
             for (int off = 1; off < DS; off <<= 1) {
                 dot_k += __shfl_xor_sync(0xffffffffu, dot_k, off);
@@ -274,7 +277,7 @@ __global__ void __launch_bounds__(128) delta_scan_rows_kernel(const float* __res
             const float2 gate = *reinterpret_cast<const float2*>(base + tt * ROW + 3 * DP);      // b, <k^, q^>
             const float u = gate.x * (vd[tt * cols] - dot_k);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
+            for (int j = 0; j < Q; ++j) {
                 S[4 * j] += kv[j].x * u; S[4 * j + 1] += kv[j].y * u; S[4 * j + 2] += kv[j].z * u; S[4 * j + 3] += kv[j].w * u;
             }
             if (s == 0 && c < vdim) o[((size_t)(t0 + tt) * H + h) * vdim + c] = dot_q + u * gate.y;
@@ -282,57 +285,59 @@ __global__ void __launch_bounds__(128) delta_scan_rows_kernel(const float* __res
         __syncthreads();                             // the buffer is fetched into again in the next round
     }
 #pragma unroll
-    for (int r = 0; r < kRows; ++r) {
+    for (int r = 0; r < R; ++r) {
         const int d = (r >> 2) * 4 * DS + 4 * s + (r & 3);
         if (d < dim && c < vdim) state[sbase + (size_t)d * vdim + c] = S[r];
     }
 }
 
-template <int DS, int TOK>
+template <int R, int DS, int TOK>
 static int launch_delta_scan_rows(const float* prepared, const float* values, float* o, float* state, const int* cu, const int* start_pos, const int* slots,
                                   const int* request_list, int num_requests, int H, int dim, int vdim, cudaStream_t stream) {
     const int threads = min(128, (vdim * DS + 31) / 32 * 32);
     const int cols = threads / DS;
     dim3 grid((vdim + cols - 1) / cols, H, num_requests);
-    const size_t smem = (size_t)2 * TOK * (3 * kRows * DS + 4 + cols) * sizeof(float);
+    const size_t smem = (size_t)2 * TOK * (3 * R * DS + 4 + cols) * sizeof(float);
     static size_t have = 0;
-    ensure_dynamic_smem(delta_scan_rows_kernel<DS, TOK>, smem, have);
-    delta_scan_rows_kernel<DS, TOK><<<grid, threads, smem, stream>>>(prepared, values, o, state, cu, start_pos, slots, request_list, H, dim, vdim);
+    ensure_dynamic_smem(delta_scan_rows_kernel<R, DS, TOK>, smem, have);
+    delta_scan_rows_kernel<R, DS, TOK><<<grid, threads, smem, stream>>>(prepared, values, o, state, cu, start_pos, slots, request_list, H, dim, vdim);
     return launch_status();
 }
 
 // The long portions of a step: the requests of `request_list` (all, if null).  Operands as in lb_delta_scan, plus
-// prepared: float32 [tokens, H, 3 DP + 4] (DP: 16 times the power of two that reaches dim) and values: float32
-// [tokens, H*vdim], both scratch.  Every token of the step is prepared, the listed requests are scanned.
+// prepared: float32 [tokens, H, 3 DP + 4] (DP: the power of two that reaches dim, 16 at least) and values: float32
+// [tokens, H*vdim], both scratch.  Every token of the step is prepared, the listed requests are scanned.  `rows`: state
+// rows a thread owns (4, 8 or 16; 0: chosen here).
 extern "C" int lb_delta_scan_rows(const void* q, const void* k, const void* v, long row_stride, const float* z, const float* dt_bias,
                                   const float* A_log, const void* beta, long beta_stride, int beta_f32, float* prepared, float* values, float* o,
                                   float* state, const int* cu, const int* start_pos, const int* slots, const int* request_list,
                                   int num_requests, long tokens, int H, int Hk, int dim, int vdim, float q_scale, float unit_eps,
-                                  int dtype, void* stream) {
+                                  int rows, int dtype, void* stream) {
     if (num_requests <= 0 || tokens <= 0) return kOk;
     if (H <= 0 || Hk <= 0 || H % Hk || dim <= 0 || vdim <= 0 || H > 65535 || num_requests > 65535) return kBadSize;
     if (dim > 512) return kTooLarge;
     cudaStream_t st = (cudaStream_t)stream;
-    int DS = 1;
-    while (kRows * DS < dim) DS <<= 1;
+    int DP = kMinPadded;
+    while (DP < dim) DP <<= 1;
+    if (rows == 0) rows = DP <= 64 ? 4 : (DP == 256 ? 8 : 16);     // measured: the fewer rows, the fewer instructions on the chain;
+                                                                   // past 64 channels the longer reduction over DS lanes outweighs it
+    if ((rows != 4 && rows != 8 && rows != 16) || DP / rows > 32) return kBadSize;
     const long pairs = tokens * H;
     const int warps = 4;
     const unsigned blocks = (unsigned)((pairs + warps - 1) / warps);
 #define LB_PREPARE(TB_) delta_prepare_kernel<T, TB_><<<blocks, warps * 32, 0, st>>>((const T*)q, (const T*)k, (const T*)v, row_stride, z, \
-        dt_bias, A_log, (const TB_*)beta, beta_stride, prepared, values, pairs, H, Hk, dim, vdim, kRows * DS, q_scale, unit_eps)
+        dt_bias, A_log, (const TB_*)beta, beta_stride, prepared, values, pairs, H, Hk, dim, vdim, DP, q_scale, unit_eps)
     LB_DISPATCH_DTYPE(dtype, { if (beta_f32) LB_PREPARE(float); else LB_PREPARE(T); });
 #undef LB_PREPARE
     const int status = launch_status();
     if (status != kOk) return status;
-#define LB_ROWS(DS_, TOK_) return launch_delta_scan_rows<DS_, TOK_>(prepared, values, o, state, cu, start_pos, slots, request_list, num_requests, \
-        H, dim, vdim, st)
-    switch (DS) {
-        case 1: LB_ROWS(1, 16);
-        case 2: LB_ROWS(2, 16);
-        case 4: LB_ROWS(4, 16);
-        case 8: LB_ROWS(8, 16);
-        case 16: LB_ROWS(16, 8);
-        default: LB_ROWS(32, 8);
+#define LB_ROWS(R_, DS_, TOK_) case (R_) * 64 + (DS_): return launch_delta_scan_rows<R_, DS_, TOK_>(prepared, values, o, state, cu, start_pos, slots, \
+        request_list, num_requests, H, dim, vdim, st)
+    switch (rows * 64 + DP / rows) {
+        LB_ROWS(4, 4, 16); LB_ROWS(4, 8, 16); LB_ROWS(4, 16, 16); LB_ROWS(4, 32, 16);
+        LB_ROWS(8, 2, 16); LB_ROWS(8, 4, 16); LB_ROWS(8, 8, 16); LB_ROWS(8, 16, 16); LB_ROWS(8, 32, 8);
+        LB_ROWS(16, 1, 16); LB_ROWS(16, 2, 16); LB_ROWS(16, 4, 16); LB_ROWS(16, 8, 16); LB_ROWS(16, 16, 8); LB_ROWS(16, 32, 8);
+        default: return kBadSize;
     }
 #undef LB_ROWS
 }

@@ -1828,7 +1828,7 @@ def delta_scan(qkv: torch.Tensor, z: torch.Tensor, dt_bias: torch.Tensor, A_log:
     return o
 
 
-DELTA_ROWS = 16         # state rows a thread of the long portions' kernel owns (kRows of csrc/delta.cu)
+DELTA_MIN_PADDED = 16   # the long portions' kernel pads key channels to a power of two, this at least (kMinPadded of csrc/delta.cu)
 
 
 def delta_scan_rows_ok(key_dim: int) -> bool:
@@ -1839,7 +1839,7 @@ def delta_scan_rows_ok(key_dim: int) -> bool:
 def delta_scan_rows(qkv: torch.Tensor, z: torch.Tensor, dt_bias: torch.Tensor, A_log: torch.Tensor, beta: torch.Tensor, state: torch.Tensor,
                     cu_seqlens: torch.Tensor, start_pos: torch.Tensor, slots: torch.Tensor, num_requests: int, num_heads: int,
                     num_key_heads: int, key_dim: int, value_dim: int, q_scale: float, unit_eps: float,
-                    request_list: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+                    request_list: torch.Tensor | None = None, out: torch.Tensor | None = None, rows_per_thread: int = 0) -> torch.Tensor:
     """`delta_scan` for portions of many tokens: one launch turns every token's unit vectors, decays and gates into 32-bit
     rows, a second one runs the recurrence of the requests of `request_list` (all, if None) with nothing but the state's
     update in its loop.  Operands and result as `delta_scan`; rows of `out` that belong to other requests are left alone."""
@@ -1863,8 +1863,8 @@ def delta_scan_rows(qkv: torch.Tensor, z: torch.Tensor, dt_bias: torch.Tensor, A
         n = request_list.numel()
     o = out if out is not None else torch.empty((T, H * dv), dtype=torch.float32, device=qkv.device)
     _need(o.dtype == torch.float32 and o.shape == (T, H * dv) and o.is_contiguous(), "out must be contiguous float32 [tokens, H*value_dim]")
-    padded = DELTA_ROWS
-    while padded < dk:                               # key channels padded to 16 times a power of two
+    padded = DELTA_MIN_PADDED
+    while padded < dk:                               # key channels padded to a power of two
         padded *= 2
     prepared = torch.empty((T, H, 3 * padded + 4), dtype=torch.float32, device=qkv.device)
     values = torch.empty((T, H * dv), dtype=torch.float32, device=qkv.device)
@@ -1872,11 +1872,11 @@ def delta_scan_rows(qkv: torch.Tensor, z: torch.Tensor, dt_bias: torch.Tensor, A
     stride = qkv.stride(0) if T > 1 else qkv.shape[1]
     f = _fn("delta", "lb_delta_scan_rows", [c_void_p, c_void_p, c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_int,
                                             c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_long,
-                                            c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p])
+                                            c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_int, c_void_p])
     _check(f(base, base + Hk * dk * item, base + 2 * Hk * dk * item, stride, _ptr(z), _ptr(dt_bias), _ptr(A_log), _ptr(beta),
              beta.stride(0) if T > 1 else max(beta.stride(0), H), int(beta.dtype == torch.float32), _ptr(prepared), _ptr(values),
              _ptr(o), _ptr(state), _ptr(cu_seqlens), _ptr(start_pos), _ptr(slots), _ptr(request_list), n, T, H, Hk, dk, dv, q_scale,
-             unit_eps, _code(qkv), _stream()), "delta_scan_rows", f"(key_dim {dk}, value_dim {dv})", launches=2)
+             unit_eps, rows_per_thread, _code(qkv), _stream()), "delta_scan_rows", f"(key_dim {dk}, value_dim {dv})", launches=2)
     return o
 
 
