@@ -137,3 +137,61 @@ def test_delta_rule_overwrites_what_a_key_held():
     o = K.delta_scan(qkv.cuda(), z.cuda(), torch.zeros(dim).cuda(), torch.zeros(1).cuda(), beta.cuda(), state.cuda(), i32(0, T), i32(0),
                      i32(0), 1, 1, 1, dim, vdim, 1.0, 1e-6)
     assert torch.allclose(o.cpu(), qkv[:, 2 * dim:], atol=1e-5)
+
+
+def slow_delta_recurrence(q, k, v, z, dt, A, beta, S, heads, kv_heads, dim, vdim):
+    """The recurrence token by token in float64, from its equations: q, k [T, kv_heads * dim], v [T, heads * vdim],
+    z [T, heads * dim], beta [T, heads]; S [heads, dim, vdim] is updated in place."""
+    T = q.shape[0]
+    o = torch.zeros(T, heads, vdim, dtype=torch.float64)
+    for t in range(T):
+        for h in range(heads):
+            hk = h // (heads // kv_heads)
+            qt, kt = q[t, hk * dim:(hk + 1) * dim], k[t, hk * dim:(hk + 1) * dim]
+            qt = qt / torch.sqrt((qt * qt).sum() + 1e-6) * dim ** -0.5
+            kt = kt / torch.sqrt((kt * kt).sum() + 1e-6)
+            g = torch.exp(-torch.exp(A[h]) * torch.nn.functional.softplus(z[t, h * dim:(h + 1) * dim] + dt[h * dim:(h + 1) * dim]))
+            S[h] = g[:, None] * S[h]
+            u = torch.sigmoid(beta[t, h]) * (v[t, h * vdim:(h + 1) * vdim] - S[h].T @ kt)
+            S[h] = S[h] + kt[:, None] * u[None, :]
+            o[t, h] = S[h].T @ qt
+    return o.reshape(T, heads * vdim)
+
+
+@pytest.mark.parametrize("heads,kv_heads,dim,vdim", [(2, 1, 5, 3), (3, 3, 24, 40), (2, 2, 64, 33), (4, 2, 100, 16), (1, 1, 128, 130), (2, 1, 300, 8)])
+@pytest.mark.parametrize("kernel", ["delta_scan", "delta_scan_rows"])
+def test_delta_rule_kernels_equal_the_recurrence_written_out(kernel, heads, kv_heads, dim, vdim):
+    """The two kernels alone: two portions side by side whose lengths are no multiples of anything, the second going on
+    from a state it is handed in another slot; decays from none to a thousandfold per token."""
+    from logssms_b200.ops import kernels as K
+    g = torch.Generator().manual_seed(dim + vdim)
+    lens = [37, 8 * 9 + 3]
+    T = sum(lens)
+    q = torch.randn(T, kv_heads * dim, generator=g, dtype=torch.float64)
+    k = torch.randn(T, kv_heads * dim, generator=g, dtype=torch.float64)
+    v = torch.randn(T, heads * vdim, generator=g, dtype=torch.float64)
+    z = torch.randn(T, heads * dim, generator=g, dtype=torch.float64) * 3.0
+    z[:, ::3] += 6.0                                # strong decays in every third channel ...
+    z[:, 1::3] -= 30.0                              # ... and none at all in the next
+    dt = torch.randn(heads * dim, generator=g, dtype=torch.float64)
+    A = torch.rand(heads, generator=g, dtype=torch.float64) * 2.0 - 1.5
+    beta = torch.randn(T, heads, generator=g, dtype=torch.float64) * 2.0
+    handed = torch.randn(heads, dim, vdim, generator=g, dtype=torch.float64)
+    want, states = [], []
+    for r, (lo, n) in enumerate(((0, lens[0]), (lens[0], lens[1]))):
+        S = torch.zeros(heads, dim, vdim, dtype=torch.float64) if r == 0 else handed.clone()
+        want.append(slow_delta_recurrence(q[lo:lo + n], k[lo:lo + n], v[lo:lo + n], z[lo:lo + n], dt, A, beta[lo:lo + n], S,
+                                          heads, kv_heads, dim, vdim))
+        states.append(S)
+    want = torch.cat(want)
+    i32 = lambda *x: torch.tensor(x, dtype=torch.int32).cuda()
+    state = torch.full((3, heads, dim, vdim), float("nan"))
+    state[2] = handed.float()                       # request 1 lives in slot 2; request 0 starts at position 0 in slot 0 (NaN there)
+    state = state.cuda()
+    qkv = torch.cat([q, k, v], 1).float().cuda()
+    o = getattr(K, kernel)(qkv, z.float().cuda(), dt.float().cuda(), A.float().cuda(), beta.float().cuda(), state, i32(0, lens[0], T),
+                           i32(0, 500), i32(0, 2), 2, heads, kv_heads, dim, vdim, dim ** -0.5, 1e-6)
+    close(o, want, torch.float32, 2e-5)
+    close(state[0], states[0], torch.float32, 2e-5)
+    close(state[2], states[1], torch.float32, 2e-5)
+    assert torch.isnan(state[1]).all()
