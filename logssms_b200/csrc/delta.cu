@@ -342,6 +342,286 @@ extern "C" int lb_delta_scan_rows(const void* q, const void* k, const void* v, l
 #undef LB_ROWS
 }
 
+// --------------------------------------------------------------------------- prompt portions in chunks of 8 tokens
+// With L_t[d] the running sum of the log-decays inside a chunk (inclusive) and S0 the state the chunk starts from,
+//     S'_t = diag(e^{L_t}) S0 + sum_{s<t} diag(e^{L_t - L_s}) k^_s u_s^T            (the state the write of token t meets)
+//     u_t  = b_t (v_t - (k^_t e^{L_t})^T S0) - sum_{s<t} A_ts u_s,     A_ts = b_t sum_d k^_t[d] k^_s[d] e^{L_t[d] - L_s[d]}
+//     o_t  = (q^_t e^{L_t})^T S0 + sum_{s<=t} B_ts u_s,                B_ts = sum_d q^_t[d] k^_s[d] e^{L_t[d] - L_s[d]}
+//     S_end = diag(e^{L_end}) S0 + sum_s (k^_s e^{L_end - L_s}) u_s^T
+// and every exponent is <= 0 whatever the decays are.  All of it is 32-bit; the sums are those of the token-by-token
+// form in another order.  What this buys: the two dot products over the key channels of ALL tokens of a chunk are
+// reduced across a column's threads in one round (their partial sums are independent), where the token-by-token form
+// has one dependent round per token.  Time follows the instructions a warp issues per token (one warp per scheduler,
+// an instruction every four cycles or so), so nothing is computed twice: the chunk's 16 sums are reduced by halving,
+// after which each of 16 lanes holds one whole sum, and u follows by forward substitution ACROSS those lanes (token j's
+// u is handed to all of them by one shuffle, each lane adds its own coefficient times it).
+//  delta_chunk_prepare : one CTA per (chunk, head), all chunks of a step side by side: the record
+//                        [q^ e^L (C x DP) | k^ e^L (C x DP) | k^ e^{L_end - L} (C x DP) | e^{L_end} (DP) | -A (C x C) | B (C x C) | b (C)]
+//                        and the head's values in 32-bit.  Tokens past the portion's end are rows of zeros with b = 0
+//                        and no decay: they change nothing.
+//  delta_chunk_scan    : a CTA owns (request, head, 128 / DS value columns) and walks the request's chunks in order; a
+//                        thread owns R = 4 or 8 state rows of one column, DS = 16 or 32 threads of a warp share a column
+//                        (DP = R DS >= 64 key channels, zeros past `dim`).  The next chunk's record arrives by cp.async
+//                        in a second buffer while this one is used.
+constexpr int kDeltaChunk = 8;
+
+template <typename T, typename TB>
+__global__ void __launch_bounds__(128) delta_chunk_prepare_kernel(
+        const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, long row_stride, const float* __restrict__ z,
+        const float* __restrict__ dt_bias, const float* __restrict__ A_log, const TB* __restrict__ beta, long beta_stride,
+        const int* __restrict__ cu, const int* __restrict__ chunks, float* __restrict__ records, float* __restrict__ values,
+        int H, int Hk, int dim, int vdim, int DP, float q_scale, float unit_eps) {
+    constexpr int C = kDeltaChunk;
+    extern __shared__ float sm[];
+    float* L = sm;                                   // [C][DP] log-decays, then their running sums
+    float* qs = L + C * DP;                          // [C][DP] unit queries (scaled)
+    float* ks = qs + C * DP;                         // [C][DP] unit keys
+    float* bs = ks + C * DP;                         // [C]
+    const int c = blockIdx.x, h = blockIdx.y, hk = h / (H / Hk);
+    const int req = chunks[2 * c];
+    if (req < 0) return;
+    const int t0 = cu[req] + chunks[2 * c + 1];
+    const int n = min(C, cu[req + 1] - t0);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    for (int j = warp; j < C; j += nwarps) {
+        float qn = 0.f, kn = 0.f;
+        const T* qr = q + (size_t)(t0 + j) * row_stride + (size_t)hk * dim;
+        const T* kr = k + (size_t)(t0 + j) * row_stride + (size_t)hk * dim;
+        if (j < n) {
+            float qq = 0.f, kk = 0.f;
+            for (int d = lane; d < dim; d += 32) {
+                const float a = to_f32(qr[d]), e = to_f32(kr[d]);
+                qq += a * a; kk += e * e;
+            }
+            qq = warp_sum(qq); kk = warp_sum(kk);
+            qn = q_scale / sqrtf(qq + unit_eps); kn = 1.f / sqrtf(kk + unit_eps);
+        }
+        for (int d = lane; d < DP; d += 32) {
+            const bool in = j < n && d < dim;
+            qs[j * DP + d] = in ? to_f32(qr[d]) * qn : 0.f;
+            ks[j * DP + d] = in ? to_f32(kr[d]) * kn : 0.f;
+        }
+        if (lane == 0) bs[j] = j < n ? 1.f / (1.f + expf(-to_f32(beta[(size_t)(t0 + j) * beta_stride + h]))) : 0.f;
+    }
+    const float rate = expf(A_log[h]);
+    for (int i = threadIdx.x; i < C * DP; i += blockDim.x) {
+        const int j = i / DP, d = i % DP;
+        L[i] = (j < n && d < dim) ? -rate * softplus_f(z[((size_t)(t0 + j) * H + h) * dim + d] + dt_bias[h * dim + d]) : 0.f;
+    }
+    __syncthreads();
+    for (int d = threadIdx.x; d < DP; d += blockDim.x) {
+        float acc = 0.f;
+        for (int j = 0; j < C; ++j) { acc += L[j * DP + d]; L[j * DP + d] = acc; }
+    }
+    __syncthreads();
+    const int REC = 3 * C * DP + DP + 2 * C * C + C;
+    float* rec = records + ((size_t)c * H + h) * REC;
+    for (int i = threadIdx.x; i < C * DP; i += blockDim.x) {
+        const int d = i % DP;
+        const float e = expf(L[i]);
+        rec[i] = qs[i] * e;
+        rec[C * DP + i] = ks[i] * e;
+        rec[2 * C * DP + i] = ks[i] * expf(L[(C - 1) * DP + d] - L[i]);
+    }
+    for (int d = threadIdx.x; d < DP; d += blockDim.x) rec[3 * C * DP + d] = expf(L[(C - 1) * DP + d]);
+    float* Ao = rec + 3 * C * DP + DP;
+    float* Bo = Ao + C * C;
+    // a warp per pair (i, j), its lanes over the key channels
+    for (int p = warp; p < C * C; p += nwarps) {
+        const int i = p / C, j = p % C;
+        float a = 0.f, b = 0.f;
+        if (j <= i) {
+            for (int d = lane; d < DP; d += 32) {
+                const float w = ks[j * DP + d] * expf(L[i * DP + d] - L[j * DP + d]);
+                a += ks[i * DP + d] * w;
+                b += qs[i * DP + d] * w;
+            }
+            a = warp_sum(a); b = warp_sum(b);
+        }
+        if (lane == 0) { Ao[p] = j < i ? -bs[i] * a : 0.f; Bo[p] = j <= i ? b : 0.f; }
+    }
+    if (threadIdx.x < C) Bo[C * C + threadIdx.x] = bs[threadIdx.x];
+    for (int i = threadIdx.x; i < n * vdim; i += blockDim.x) {
+        const int j = i / vdim, cc = i % vdim;
+        values[((size_t)(t0 + j) * H + h) * vdim + cc] = to_f32(v[(size_t)(t0 + j) * row_stride + (size_t)h * vdim + cc]);
+    }
+}
+
+// grid (ceil(vdim / (128 / DS)), H, requests with long portions); per_request: (request, its first chunk, its chunks)
+template <int R, int DS>
+__global__ void __launch_bounds__(128) delta_chunk_scan_kernel(const float* __restrict__ records, const float* __restrict__ values,
+                                                               float* __restrict__ o, float* state, const int* __restrict__ cu,
+                                                               const int* __restrict__ start_pos, const int* __restrict__ slots,
+                                                               const int* __restrict__ per_request, int H, int dim, int vdim) {
+    constexpr int C = kDeltaChunk, DP = R * DS, Q = R / 4, REC = 3 * C * DP + DP + 2 * C * C + C, PIECES = REC / 4, cols = 128 / DS;
+    extern __shared__ __align__(16) float sm[];
+    float* recs = sm;                                // [2][REC]
+    float* vals = sm + 2 * REC;                      // [2][C][cols]
+    const int req = per_request[3 * blockIdx.z];
+    if (req < 0) return;
+    const int chunk0 = per_request[3 * blockIdx.z + 1], nchunks = per_request[3 * blockIdx.z + 2];
+    const int h = blockIdx.y;
+    const int col_local = threadIdx.x / DS, s = threadIdx.x % DS;
+    const int c = blockIdx.x * cols + col_local;
+    const int first = cu[req], last = cu[req + 1];
+    const size_t sbase = ((size_t)slots[req] * H + h) * dim * vdim;
+    const bool fresh = start_pos[req] == 0;
+    float S[R];                                      // rows interleaved in fours: row 4 DS j + 4 s + i, as in delta_scan_rows
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        const int d = (r >> 2) * 4 * DS + 4 * s + (r & 3);
+        S[r] = (!fresh && d < dim && c < vdim) ? state[sbase + (size_t)d * vdim + c] : 0.f;
+    }
+    auto fetch = [&](int ci, int buf) {
+        const float* src = records + ((size_t)(chunk0 + ci) * H + h) * REC;
+        float* dst = recs + buf * REC;
+        for (int i = threadIdx.x; i < PIECES; i += blockDim.x) delta_cp16(dst + 4 * i, src + 4 * i);
+        const int t0 = first + ci * C, n = min(C, last - t0);
+        float* vd = vals + buf * C * cols;
+        for (int i = threadIdx.x; i < C * cols; i += blockDim.x) {
+            const int tt = i / cols, cc = blockIdx.x * cols + i % cols;
+            if (tt < n && cc < vdim) delta_cp4(vd + i, values + ((size_t)(t0 + tt) * H + h) * vdim + cc);
+            else vd[i] = 0.f;
+        }
+        delta_cp_commit();
+    };
+    fetch(0, 0);
+    int buf = 0;
+    for (int ci = 0; ci < nchunks; ++ci, buf ^= 1) {
+        if (ci + 1 < nchunks) { fetch(ci + 1, buf ^ 1); delta_cp_wait<1>(); } else { delta_cp_wait<0>(); }
+        __syncthreads();
+        const int t0 = first + ci * C, n = min(C, last - t0);
+        const float* rec = recs + buf * REC;
+        const float4* Qt = reinterpret_cast<const float4*>(rec) + s;
+        const float4* Kt = Qt + C * DP / 4;
+        const float4* Kb = Kt + C * DP / 4;
+        const float4* G4 = reinterpret_cast<const float4*>(rec + 3 * C * DP) + s;
+        const float* be = rec + 3 * C * DP + DP + 2 * C * C;
+        const float* vd = vals + buf * C * cols + col_local;
+        float p[C], e[C], u[C];
+#pragma unroll
+        for (int t = 0; t < C; ++t) {
+            float pp = 0.f, ee = 0.f;
+#pragma unroll
+            for (int j = 0; j < Q; ++j) {
+                const float4 kt = Kt[t * (DP / 4) + j * DS], qt = Qt[t * (DP / 4) + j * DS];
+                pp += (kt.x * S[4 * j] + kt.y * S[4 * j + 1]) + (kt.z * S[4 * j + 2] + kt.w * S[4 * j + 3]);
+                ee += (qt.x * S[4 * j] + qt.y * S[4 * j + 1]) + (qt.z * S[4 * j + 2] + qt.w * S[4 * j + 3]);
+            }
+            p[t] = pp; e[t] = ee;
+        }
+        // The 16 sums (8 tokens x {<S, k^ e^L>, <S, q^ e^L>}) are reduced over the column's lanes by halving: in every stage a
+        // lane keeps half of its values and hands the other half to its partner, so that lane l of 16 ends with the whole
+        // sum number l (lanes 0-7: token l's key product, lanes 8-15: token l - 8's query product).
+        if (DS == 32) {
+#pragma unroll
+            for (int t = 0; t < C; ++t) {
+                p[t] += __shfl_xor_sync(0xffffffffu, p[t], 16);
+                e[t] += __shfl_xor_sync(0xffffffffu, e[t], 16);
+            }
+        }
+        const int sl = s & 15, tk = sl & 7;
+        const bool reads = sl >= 8;                    // this lane ends with a read-out (else with a write's size)
+        float y8[8], y4[4], y2[2], w;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) y8[i] = (reads ? e[i] : p[i]) + __shfl_xor_sync(0xffffffffu, reads ? p[i] : e[i], 8);
+        {
+            const bool up = sl & 4;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) y4[i] = (up ? y8[i + 4] : y8[i]) + __shfl_xor_sync(0xffffffffu, up ? y8[i] : y8[i + 4], 4);
+        }
+        {
+            const bool up = sl & 2;
+#pragma unroll
+            for (int i = 0; i < 2; ++i) y2[i] = (up ? y4[i + 2] : y4[i]) + __shfl_xor_sync(0xffffffffu, up ? y4[i] : y4[i + 2], 2);
+        }
+        {
+            const bool up = sl & 1;
+            w = (up ? y2[1] : y2[0]) + __shfl_xor_sync(0xffffffffu, up ? y2[0] : y2[1], 1);
+        }
+        // Forward substitution across the lanes: lane t < 8 starts from b_t (v_t - <S0, k^_t e^L>) and lane 8 + t from token t's
+        // read-out of S0; token j's finished u is handed to everyone (all lanes need it for the state), and every lane adds
+        // its own coefficient times it: -A[t][j] (zero from the diagonal on) or B[t][j] (zero past the diagonal).
+        if (!reads) w = be[tk] * (vd[tk * cols] - w);
+        float row[C];
+        {
+            const float4* rp = reinterpret_cast<const float4*>(rec + 3 * C * DP + DP + (reads ? C * C : 0) + tk * C);
+            const float4 r0 = rp[0], r1 = rp[1];
+            row[0] = r0.x; row[1] = r0.y; row[2] = r0.z; row[3] = r0.w; row[4] = r1.x; row[5] = r1.y; row[6] = r1.z; row[7] = r1.w;
+        }
+        const int base = (threadIdx.x & 31) & ~(DS - 1);
+#pragma unroll
+        for (int j = 0; j < C; ++j) {
+            u[j] = __shfl_sync(0xffffffffu, w, base | j);
+            w = fmaf(row[j], u[j], w);
+        }
+        if (reads && s < 16 && c < vdim && tk < n) o[((size_t)(t0 + tk) * H + h) * vdim + c] = w;
+#pragma unroll
+        for (int j = 0; j < Q; ++j) {
+            const float4 g = G4[j * DS];
+            S[4 * j] *= g.x; S[4 * j + 1] *= g.y; S[4 * j + 2] *= g.z; S[4 * j + 3] *= g.w;
+#pragma unroll
+            for (int t = 0; t < C; ++t) {
+                const float4 kb = Kb[t * (DP / 4) + j * DS];
+                S[4 * j] += kb.x * u[t]; S[4 * j + 1] += kb.y * u[t]; S[4 * j + 2] += kb.z * u[t]; S[4 * j + 3] += kb.w * u[t];
+            }
+        }
+        __syncthreads();                             // the buffer is fetched into again in the next round
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        const int d = (r >> 2) * 4 * DS + 4 * s + (r & 3);
+        if (d < dim && c < vdim) state[sbase + (size_t)d * vdim + c] = S[r];
+    }
+}
+
+template <int R, int DS>
+static int launch_delta_chunk_scan(const float* records, const float* values, float* o, float* state, const int* cu, const int* start_pos,
+                                   const int* slots, const int* per_request, int num_long, int H, int dim, int vdim, cudaStream_t stream) {
+    constexpr int C = kDeltaChunk, DP = R * DS, REC = 3 * C * DP + DP + 2 * C * C + C, cols = 128 / DS;
+    dim3 grid((vdim + cols - 1) / cols, H, num_long);
+    const size_t smem = (size_t)2 * (REC + C * cols) * sizeof(float);
+    static size_t have = 0;
+    ensure_dynamic_smem(delta_chunk_scan_kernel<R, DS>, smem, have);
+    delta_chunk_scan_kernel<R, DS><<<grid, 128, smem, stream>>>(records, values, o, state, cu, start_pos, slots, per_request, H, dim, vdim);
+    return launch_status();
+}
+
+// The long portions of a step in chunks of 8 tokens (up to 256 key channels).  Operands as in lb_delta_scan, plus the work
+// lists chunks: int32 [num_chunks, 2] (request, first token of the chunk within its portion; request -1: skipped) and
+// per_request: int32 [num_long, 3] (request, its first chunk, its chunks; -1: skipped); records: float32 [num_chunks, H,
+// 24 DP + DP + 136] (DP: the power of two that reaches dim, 64 at least) and values: float32 [tokens, H*vdim], both scratch.
+// `rows`: state rows a thread owns (4 or 8; 0: chosen here).
+extern "C" int lb_delta_scan_chunks(const void* q, const void* k, const void* v, long row_stride, const float* z, const float* dt_bias,
+                                    const float* A_log, const void* beta, long beta_stride, int beta_f32, float* records, float* values,
+                                    float* o, float* state, const int* cu, const int* start_pos, const int* slots, const int* chunks,
+                                    int num_chunks, const int* per_request, int num_long, int H, int Hk, int dim, int vdim, float q_scale,
+                                    float unit_eps, int rows, int dtype, void* stream) {
+    if (num_chunks <= 0 || num_long <= 0) return kOk;
+    if (H <= 0 || Hk <= 0 || H % Hk || dim <= 0 || vdim <= 0 || H > 65535 || num_long > 65535) return kBadSize;
+    if (dim > 256) return kTooLarge;
+    cudaStream_t st = (cudaStream_t)stream;
+    int DP = 64;                                     // a column is shared by 16 or 32 lanes of 4 or 8 rows each
+    while (DP < dim) DP <<= 1;
+    const size_t smem = (size_t)(3 * kDeltaChunk * DP + kDeltaChunk) * sizeof(float);
+    dim3 grid(num_chunks, H);
+#define LB_PREPARE(TB_) delta_chunk_prepare_kernel<T, TB_><<<grid, 128, smem, st>>>((const T*)q, (const T*)k, (const T*)v, row_stride, z, \
+        dt_bias, A_log, (const TB_*)beta, beta_stride, cu, chunks, records, values, H, Hk, dim, vdim, DP, q_scale, unit_eps)
+    LB_DISPATCH_DTYPE(dtype, { if (beta_f32) LB_PREPARE(float); else LB_PREPARE(T); });
+#undef LB_PREPARE
+    const int status = launch_status();
+    if (status != kOk) return status;
+    if (rows == 0) rows = DP <= 64 ? 4 : 8;           // measured at 128 channels: 8 rows on 16 lanes beat 4 rows on 32
+    if ((rows != 4 && rows != 8) || (DP / rows != 16 && DP / rows != 32)) return kBadSize;
+#define LB_CHUNKS(R_, DS_) case (R_) * 64 + (DS_): return launch_delta_chunk_scan<R_, DS_>(records, values, o, state, cu, start_pos, slots, \
+        per_request, num_long, H, dim, vdim, st)
+    switch (rows * 64 + DP / rows) {
+        LB_CHUNKS(4, 16); LB_CHUNKS(4, 32); LB_CHUNKS(8, 16); LB_CHUNKS(8, 32);
+        default: return kBadSize;
+    }
+#undef LB_CHUNKS
+}
+
 // q, k: [tokens, Hk*dim] and v: [tokens, H*vdim], column views of one buffer (common row stride, in elements);
 // z: float32 [tokens, H*dim]; dt_bias: float32 [H*dim]; A_log: float32 [H]; beta: [tokens, >= H] logits of the write's
 // gate (float32 with `beta_f32`, else the activation dtype; row stride in elements); o: float32 [tokens, H*vdim];

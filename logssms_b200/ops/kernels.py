@@ -1880,6 +1880,59 @@ def delta_scan_rows(qkv: torch.Tensor, z: torch.Tensor, dt_bias: torch.Tensor, A
     return o
 
 
+DELTA_CHUNK = 8         # tokens per chunk of the chunked form (kDeltaChunk of csrc/delta.cu)
+
+
+def delta_scan_chunks_ok(key_dim: int) -> bool:
+    """Does the chunked kernel of long portions take this many key channels?"""
+    return 0 < key_dim <= 256
+
+
+def delta_scan_chunks(qkv: torch.Tensor, z: torch.Tensor, dt_bias: torch.Tensor, A_log: torch.Tensor, beta: torch.Tensor, state: torch.Tensor,
+                      cu_seqlens: torch.Tensor, start_pos: torch.Tensor, slots: torch.Tensor, chunks: torch.Tensor, num_chunks: int,
+                      per_request: torch.Tensor, num_long: int, num_heads: int, num_key_heads: int, key_dim: int, value_dim: int,
+                      q_scale: float, unit_eps: float, out: torch.Tensor | None = None, rows_per_thread: int = 0) -> torch.Tensor:
+    """`delta_scan` for the long portions of a step in chunks of `DELTA_CHUNK` tokens: one launch turns every chunk into a
+    32-bit record (unit vectors times the chunk's running decays, the two small triangular matrices between its tokens), a
+    second one walks each listed request's chunks with one reduction round per chunk (the 16 sums of a chunk reduced by
+    halving over the lanes that share a value column, the writes' sizes by forward substitution across those lanes).  `chunks` int32 [num_chunks, 2] and
+    `per_request` int32 [num_long, 3] are the work lists of `StepContext.long_portion_chunks(DELTA_CHUNK)`.  Operands and
+    result as `delta_scan`; rows of `out` that belong to other requests are left alone."""
+    _cuda(qkv, z, dt_bias, A_log, beta, state, cu_seqlens, start_pos, slots, chunks, per_request)
+    H, Hk, dk, dv = num_heads, num_key_heads, key_dim, value_dim
+    T = qkv.shape[0]
+    _need(delta_scan_chunks_ok(dk), "delta_scan_chunks takes up to 256 key channels")
+    _need(qkv.dim() == 2 and qkv.stride(1) == 1 and qkv.shape[1] >= 2 * Hk * dk + H * dv, "qkv must hold the columns q | k | v")
+    _need(z.dtype == torch.float32 and z.shape == (T, H * dk) and z.is_contiguous(), "z must be contiguous float32 [tokens, H*key_dim]")
+    _need(dt_bias.dtype == torch.float32 and dt_bias.numel() == H * dk and dt_bias.is_contiguous() and A_log.dtype == torch.float32
+          and A_log.shape == (H,) and A_log.is_contiguous(), "dt_bias float32 [H*key_dim], A_log float32 [H]")
+    _need(beta.dim() == 2 and beta.shape == (T, H) and beta.stride(1) == 1 and beta.dtype in (torch.float32, qkv.dtype),
+          "beta must be [tokens, H] in float32 or the activation dtype")
+    _need(state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (H, dk, dv),
+          "the state must be contiguous float32 [slots, H, key_dim, value_dim]")
+    for t, name in ((cu_seqlens, "cu_seqlens"), (start_pos, "start_pos"), (slots, "slots"), (chunks, "chunks"), (per_request, "per_request")):
+        _i32(t, name)
+    _need(chunks.numel() >= 2 * num_chunks and per_request.numel() >= 3 * num_long, "work lists shorter than their counts")
+    o = out if out is not None else torch.empty((T, H * dv), dtype=torch.float32, device=qkv.device)
+    _need(o.dtype == torch.float32 and o.shape == (T, H * dv) and o.is_contiguous(), "out must be contiguous float32 [tokens, H*value_dim]")
+    padded = 64                                      # 16 or 32 lanes of a warp share a column, 4 or 8 rows each
+    while padded < dk:                               # key channels padded to a power of two
+        padded *= 2
+    C = DELTA_CHUNK
+    records = torch.empty((max(num_chunks, 1), H, 3 * C * padded + padded + 2 * C * C + C), dtype=torch.float32, device=qkv.device)
+    values = torch.empty((T, H * dv), dtype=torch.float32, device=qkv.device)
+    item, base = qkv.element_size(), qkv.data_ptr()
+    stride = qkv.stride(0) if T > 1 else qkv.shape[1]
+    f = _fn("delta", "lb_delta_scan_chunks", [c_void_p, c_void_p, c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_int,
+                                              c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                              c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_int, c_void_p])
+    _check(f(base, base + Hk * dk * item, base + 2 * Hk * dk * item, stride, _ptr(z), _ptr(dt_bias), _ptr(A_log), _ptr(beta),
+             beta.stride(0) if T > 1 else max(beta.stride(0), H), int(beta.dtype == torch.float32), _ptr(records), _ptr(values),
+             _ptr(o), _ptr(state), _ptr(cu_seqlens), _ptr(start_pos), _ptr(slots), _ptr(chunks), num_chunks, _ptr(per_request), num_long,
+             H, Hk, dk, dv, q_scale, unit_eps, rows_per_thread, _code(qkv), _stream()), "delta_scan_chunks", f"(key_dim {dk}, value_dim {dv})", launches=2)
+    return o
+
+
 # --------------------------------------------------------------------------- a 32-bit stream whose sublayers all read one norm
 def stream_add_many(x: torch.Tensor, addends, weight: torch.Tensor | None, eps: float, kind: str,
                     act_dtype: torch.dtype) -> tuple[torch.Tensor, torch.Tensor | None]:

@@ -27,7 +27,8 @@ class ChannelDelta(Part):
     Per-request state: the convolution's last taps - 1 inputs per channel (activation dtype) and S [heads, key_dim,
     value_dim] in float32.  The six input products are one (rows q | k | v | a1 | g1 | b, merged at bind time); the unit
     vectors, decays, gates, the state and the head norm are 32-bit in every engine dtype (`K.delta_scan` token by token for
-    decoded tokens and short portions, `K.delta_scan_rows` for long portions).
+    decoded tokens and short portions, `K.delta_scan_chunks` for long portions, `K.delta_scan_rows` for those past 256 key
+    channels).
     Tensors: q, q.conv, k, k.conv, v, v.conv, b, A_log, dt_bias, a1, a2, g1, g2, norm, o."""
     kernels = ("delta", "conv", "gla", "moe", "linear_skinny", "gemm_tcgen05")
 
@@ -100,11 +101,16 @@ class ChannelDelta(Part):
         beta = proj[:, C + ra + rg:]
         args = (conv, z, self.dt_bias, self.A_log, beta, states["delta"], ctx.cu_seqlens, ctx.start_pos, ctx.slots, ctx.num_requests,
                 H, Hk, dk, dv, dk ** -0.5, s.unit_eps)
-        if ctx.has_long_portions and K.delta_scan_rows_ok(dk):
-            # long portions: the rows that the recurrence reads are made for all tokens at once, its loop holds the state's
-            # update alone; decoded tokens and short portions beside them token by token
+        if ctx.has_long_portions and (K.delta_scan_chunks_ok(dk) or K.delta_scan_rows_ok(dk)):
+            # long portions: what the recurrence reads is made for all tokens at once (in chunks of tokens that share one
+            # reduction round, or, past 256 key channels, token by token with the state's update alone in the loop);
+            # decoded tokens and short portions beside them token by token
             long_list, _, short_list, n_short = ctx.requests_by_portion()
-            o = K.delta_scan_rows(*args, request_list=long_list)
+            if K.delta_scan_chunks_ok(dk):
+                chunks, n_chunks, per_request, n_long = ctx.long_portion_chunks(K.DELTA_CHUNK)
+                o = K.delta_scan_chunks(*args[:9], chunks, n_chunks, per_request, n_long, *args[10:])
+            else:
+                o = K.delta_scan_rows(*args, request_list=long_list)
             if n_short > 0:
                 K.delta_scan(*args, request_list=short_list, out=o)
         else:

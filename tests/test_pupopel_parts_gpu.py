@@ -158,12 +158,16 @@ def slow_delta_recurrence(q, k, v, z, dt, A, beta, S, heads, kv_heads, dim, vdim
     return o.reshape(T, heads * vdim)
 
 
-@pytest.mark.parametrize("heads,kv_heads,dim,vdim", [(2, 1, 5, 3), (3, 3, 24, 40), (2, 2, 64, 33), (4, 2, 100, 16), (1, 1, 128, 130), (2, 1, 300, 8)])
-@pytest.mark.parametrize("kernel", ["delta_scan", "delta_scan_rows"])
+@pytest.mark.parametrize("heads,kv_heads,dim,vdim", [(2, 1, 5, 3), (3, 3, 24, 40), (2, 2, 64, 33), (4, 2, 100, 16), (1, 1, 128, 130), (1, 1, 200, 9), (2, 1, 300, 8)])
+@pytest.mark.parametrize("kernel", ["delta_scan", "delta_scan_rows", "delta_scan_chunks"])
 def test_delta_rule_kernels_equal_the_recurrence_written_out(kernel, heads, kv_heads, dim, vdim):
-    """The two kernels alone: two portions side by side whose lengths are no multiples of anything, the second going on
-    from a state it is handed in another slot; decays from none to a thousandfold per token."""
+    """The three kernels alone: two portions side by side whose lengths are no multiples of anything, the second going on
+    from a state it is handed in another slot; decays from none to a thousandfold per token (a chunk's running decay
+    underflows in some channels, so only differences of log-decays may ever be exponentiated)."""
     from logssms_b200.ops import kernels as K
+    from logssms_b200.parts.context import chunk_lists
+    if kernel == "delta_scan_chunks" and not K.delta_scan_chunks_ok(dim):
+        pytest.skip("more key channels than the chunked kernel takes")
     g = torch.Generator().manual_seed(dim + vdim)
     lens = [37, 8 * 9 + 3]
     T = sum(lens)
@@ -189,8 +193,14 @@ def test_delta_rule_kernels_equal_the_recurrence_written_out(kernel, heads, kv_h
     state[2] = handed.float()                       # request 1 lives in slot 2; request 0 starts at position 0 in slot 0 (NaN there)
     state = state.cuda()
     qkv = torch.cat([q, k, v], 1).float().cuda()
-    o = getattr(K, kernel)(qkv, z.float().cuda(), dt.float().cuda(), A.float().cuda(), beta.float().cuda(), state, i32(0, lens[0], T),
-                           i32(0, 500), i32(0, 2), 2, heads, kv_heads, dim, vdim, dim ** -0.5, 1e-6)
+    common = (qkv, z.float().cuda(), dt.float().cuda(), A.float().cuda(), beta.float().cuda(), state, i32(0, lens[0], T), i32(0, 500), i32(0, 2))
+    sizes = (heads, kv_heads, dim, vdim, dim ** -0.5, 1e-6)
+    if kernel == "delta_scan_chunks":
+        chunks, per_request = chunk_lists(lens, K.DELTA_CHUNK)
+        o = K.delta_scan_chunks(*common, torch.from_numpy(chunks).cuda(), chunks.shape[0], torch.from_numpy(per_request).cuda(),
+                                per_request.shape[0], *sizes)
+    else:
+        o = getattr(K, kernel)(*common, 2, *sizes)
     close(o, want, torch.float32, 2e-5)
     close(state[0], states[0], torch.float32, 2e-5)
     close(state[2], states[1], torch.float32, 2e-5)
