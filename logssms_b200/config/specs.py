@@ -121,6 +121,11 @@ class LatentAttentionSpec:
     position: RopeSpec | None       # rotation of the first `position.rotary_dim` dims of the rotated part
     norm_eps: float
     kind: str = "latent_attention"
+    pairing: str = "halves"         # the rotation pairs column i with i + n/2 ("halves") or 2i with 2i + 1 ("neighbours")
+    sink: bool = False              # a stored number per head joins the softmax's denominator as exp(sink_h)
+    head_gate: bool = False         # a head's output is multiplied by sigmoid of a projection of the input, one number per head
+    own_latents: bool = True        # False: no down-projection; the layer reads the latents another layer cached
+                                    # (the schedule gives it that layer's cache, `writes_cache=False`)
 
 
 @dataclass(frozen=True)
@@ -219,6 +224,46 @@ class SinkAttentionSpec:
     slope_span: float = 8.0
     sink: bool = True
     kind: str = "sink_attention"
+
+
+@dataclass(frozen=True)
+class ConvAttentionSpec:
+    """Grouped-query attention over a sliding window whose values are its keys: q and k pass a short causal convolution per
+    channel (`conv_kernel` taps, no activation); v is k as it leaves the convolution; q and k are then each RMS-normed over
+    their whole row (all heads at once, a weight per column), rotated over neighbouring pairs of every head's first
+    `position.rotary_dim` columns; scores times `softmax_scale`, position i sees j with 0 <= i - j < window (None: every
+    j <= i); with `sink` a stored number per head joins the softmax's denominator; with `head_gate` a head's output is
+    multiplied by sigmoid of a projection of the input."""
+    hidden_size: int
+    num_heads: int
+    num_kv_heads: int
+    head_dim: int
+    conv_kernel: int
+    softmax_scale: float
+    window: int | None
+    position: RopeSpec | None
+    norm_eps: float
+    sink: bool = True
+    head_gate: bool = True
+    kind: str = "conv_attention"
+
+
+@dataclass(frozen=True)
+class GatedDeltaSpec:
+    """Gated delta rule with one decay per head: q, k (`num_key_heads` heads of `key_dim`) and v (`num_heads` heads of
+    `value_dim`) pass a short causal convolution of `conv_kernel` taps and silu; q and k become unit vectors per head
+    (x / sqrt(|x|^2 + unit_eps), q also times key_dim^-1/2); per head S <- g S, u = b (v - S^T k), S <- S + k u^T, o = S^T q
+    with g = exp(-exp(A_log) softplus(projection + dt_bias)) and b = sigmoid(projection), one number per head each; o is
+    RMS-normed per head (one weight for all heads), times silu of a gate projection, then the output projection."""
+    hidden_size: int
+    num_heads: int
+    num_key_heads: int
+    key_dim: int
+    value_dim: int
+    conv_kernel: int
+    norm_eps: float
+    unit_eps: float = 1e-6
+    kind: str = "gated_delta"
 
 
 @dataclass(frozen=True)
@@ -324,6 +369,21 @@ class PostNormBlockSpec:
     feed_forward_norm_name: str
     skip_scale: float = 1.0
     kind: str = "postnorm"
+
+
+@dataclass(frozen=True)
+class OutNormBlockSpec:
+    """Block on a 32-bit stream whose norms sit on the sublayers' outputs alone: x <- x + norm1(mixer(x)), then, when it has a
+    feed-forward, x <- x + norm2(feed_forward(x)).  The sublayers read the stream itself."""
+    prefix: str
+    mixer: MixerSlot
+    mixer_norm: NormSpec
+    mixer_norm_name: str
+    feed_forward: Any                 # None: no feed-forward sublayer (and no second norm)
+    feed_forward_name: str
+    feed_forward_norm: NormSpec | None
+    feed_forward_norm_name: str
+    kind: str = "outnorm_stream"
 
 
 @dataclass(frozen=True)

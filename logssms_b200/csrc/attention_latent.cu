@@ -15,33 +15,40 @@
 #include "lb200/common.cuh"
 using namespace lb200;
 
-// grid (tokens); the rotation pairs column i with i + rd/2 among the first rd columns of a rotated part
+// grid (tokens); the rotation pairs column i with i + rd/2 among the first rd columns of a rotated part, or, with
+// `neighbours`, column 2i with 2i + 1.  Without `write_cache` the row holds the queries alone (a layer that reads the
+// latents another layer cached has no down-projection).
 template <typename T>
 __global__ void latent_prepare_kernel(T* proj, long row_stride, int q_cols, int H, int nope, int rot, int rank,
                                       const int* __restrict__ positions, const int* __restrict__ slot_mapping,
                                       const float* __restrict__ cos_sin, int table_rows, int rd,
                                       const float* __restrict__ norm_w, float eps, T* __restrict__ c_cache,
-                                      T* __restrict__ kr_cache, int write_cache) {
+                                      T* __restrict__ kr_cache, int write_cache, int neighbours) {
     __shared__ float red[32];
     const size_t t = blockIdx.x;
     T* row = proj + t * row_stride;
     const int pos = min(max(positions[t], 0), table_rows - 1);
     const float* cs = cos_sin + (size_t)pos * rd;
     const int half = rd >> 1;
-    const size_t slot = (size_t)slot_mapping[t];
-    // latent: RMSNorm in 32-bit
-    const T* d = row + q_cols;
-    float ss = 0.f;
-    for (int i = threadIdx.x; i < rank; i += blockDim.x) { const float v = to_f32(d[i]); ss += v * v; }
-    ss = block_sum(ss, red);
-    const float inv = 1.f / sqrtf(ss / (float)rank + eps);
-    if (write_cache) {
+    if (write_cache) {                                        // (uniform over the grid: no thread skips the reduction)
+        const size_t slot = (size_t)slot_mapping[t];
+        // latent: RMSNorm in 32-bit
+        const T* d = row + q_cols;
+        float ss = 0.f;
+        for (int i = threadIdx.x; i < rank; i += blockDim.x) { const float v = to_f32(d[i]); ss += v * v; }
+        ss = block_sum(ss, red);
+        const float inv = 1.f / sqrtf(ss / (float)rank + eps);
         for (int i = threadIdx.x; i < rank; i += blockDim.x) c_cache[slot * rank + i] = from_f32<T>(to_f32(d[i]) * inv * norm_w[i]);
         // the shared rotated key part
         const T* kr = d + rank;
         for (int i = threadIdx.x; i < rot; i += blockDim.x) {
             float v = to_f32(kr[i]);
-            if (i < half) v = v * cs[i] - to_f32(kr[i + half]) * cs[half + i];
+            if (neighbours) {
+                if (i < rd) {
+                    const float partner = to_f32(kr[i ^ 1]), co = cs[i >> 1], si = cs[half + (i >> 1)];
+                    v = (i & 1) ? v * co + partner * si : v * co - partner * si;
+                }
+            } else if (i < half) v = v * cs[i] - to_f32(kr[i + half]) * cs[half + i];
             else if (i < rd) v = v * cs[i - half] + to_f32(kr[i - half]) * cs[i];
             kr_cache[slot * rot + i] = from_f32<T>(v);
         }
@@ -50,21 +57,22 @@ __global__ void latent_prepare_kernel(T* proj, long row_stride, int q_cols, int 
     for (int i = threadIdx.x; i < H * half; i += blockDim.x) {
         const int h = i / half, j = i % half;
         T* qr = row + (size_t)h * (nope + rot) + nope;
-        const float u = to_f32(qr[j]), w = to_f32(qr[j + half]);
-        qr[j] = from_f32<T>(u * cs[j] - w * cs[half + j]);
-        qr[j + half] = from_f32<T>(w * cs[j] + u * cs[half + j]);
+        const int a = neighbours ? 2 * j : j, b = neighbours ? 2 * j + 1 : j + half;
+        const float u = to_f32(qr[a]), w = to_f32(qr[b]);
+        qr[a] = from_f32<T>(u * cs[j] - w * cs[half + j]);
+        qr[b] = from_f32<T>(w * cs[j] + u * cs[half + j]);
     }
 }
 
 extern "C" int lb_latent_prepare(void* proj, long row_stride, int q_cols, int H, int nope, int rot, int rank,
                                  const int* positions, const int* slot_mapping, const float* cos_sin, int table_rows, int rd,
-                                 const float* norm_w, float eps, void* c_cache, void* kr_cache, int write_cache, int tokens,
-                                 int dtype, void* stream) {
+                                 const float* norm_w, float eps, void* c_cache, void* kr_cache, int write_cache, int neighbours,
+                                 int tokens, int dtype, void* stream) {
     if (tokens <= 0) return kOk;
     if (H <= 0 || nope < 0 || rot < 0 || rank <= 0 || rd < 0 || rd > rot || (rd & 1)) return kBadSize;
     LB_DISPATCH_DTYPE(dtype, latent_prepare_kernel<T><<<tokens, 128, 0, (cudaStream_t)stream>>>(
         (T*)proj, row_stride, q_cols, H, nope, rot, rank, positions, slot_mapping, cos_sin, table_rows, rd, norm_w, eps,
-        (T*)c_cache, (T*)kr_cache, write_cache));
+        (T*)c_cache, (T*)kr_cache, write_cache, neighbours));
     return launch_status();
 }
 
@@ -137,7 +145,7 @@ __global__ void __launch_bounds__(kLaWarps * 32) latent_attention_kernel(
         const T* __restrict__ qa, const T* __restrict__ q_rot, long q_rot_row, long q_rot_head,
         const T* __restrict__ c_cache, const T* __restrict__ kr_cache, const int* __restrict__ block_table, int table_width,
         const int* __restrict__ token_req, const int* __restrict__ positions, const int* __restrict__ token_list,
-        T* __restrict__ out, int H, int rank, int rot, int page_size, float scale, int window) {
+        T* __restrict__ out, int H, int rank, int rot, int page_size, float scale, int window, const float* __restrict__ sinks) {
     extern __shared__ float sm[];
     const int D = rank + rot, DP = D + 1;
     float* qs = sm;                        // [kLaWarps][D]
@@ -194,6 +202,7 @@ __global__ void __launch_bounds__(kLaWarps * 32) latent_attention_kernel(
         m = m_new;
     }
     if (!live) return;
+    if (sinks != nullptr) l += expf(sinks[h] - m);             // the sink: one more term of the denominator, no key, no value
     const float inv = 1.f / l;
 #pragma unroll
     for (int i = 0; i < kLaMaxPieces; ++i)
@@ -205,7 +214,7 @@ __global__ void __launch_bounds__(kLaWarps * 32) latent_attention_kernel(
 extern "C" int lb_latent_attention(const void* qa, const void* q_rot, long q_rot_row, long q_rot_head, const void* c_cache,
                                    const void* kr_cache, const int* block_table, int table_width, const int* token_req,
                                    const int* positions, const int* token_list, int num_listed, void* out, int H, int rank,
-                                   int rot, int page_size, float scale, int window, int dtype, void* stream) {
+                                   int rot, int page_size, float scale, int window, const float* sinks, int dtype, void* stream) {
     if (num_listed <= 0) return kOk;
     if (H <= 0 || rank <= 0 || rot < 0 || page_size <= 0 || window < 0) return kBadSize;
     if (rank > 32 * kLaMaxPieces) return kTooLarge;
@@ -218,7 +227,7 @@ extern "C" int lb_latent_attention(const void* qa, const void* q_rot, long q_rot
         ensure_dynamic_smem(latent_attention_kernel<T>, smem, have);
         latent_attention_kernel<T><<<grid, kLaWarps * 32, smem, (cudaStream_t)stream>>>(
             (const T*)qa, (const T*)q_rot, q_rot_row, q_rot_head, (const T*)c_cache, (const T*)kr_cache, block_table,
-            table_width, token_req, positions, token_list, (T*)out, H, rank, rot, page_size, scale, window);
+            table_width, token_req, positions, token_list, (T*)out, H, rank, rot, page_size, scale, window, sinks);
     });
     return launch_status();
 }
@@ -275,7 +284,7 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(
         const int* __restrict__ block_table, int table_width, const int* __restrict__ token_req,
         const int* __restrict__ positions, const int* __restrict__ blocks, __nv_bfloat16* __restrict__ out,
         float* __restrict__ part_o, float* __restrict__ part_ml, int H, int rank, int rot, int page_size, float scale,
-        int window, int splits) {
+        int window, int splits, const float* __restrict__ sinks) {
     typedef __nv_bfloat16 bf;
     extern __shared__ __align__(16) unsigned char raw[];
     const int D = rank + rot, DP = D + 8, PP = kMmaKeys + 8;
@@ -435,9 +444,10 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(
     for (int e = 0; e < 2; ++e) {
         const int r = g + 8 * e, tok = r / nh, h = h0 + r % nh;
         if (tok >= ntok) continue;
-        const float lt = red[r] + red[16 + r] + red[32 + r] + red[48 + r];
+        float lt = red[r] + red[16 + r] + red[32 + r] + red[48 + r];
         const size_t row = (size_t)(t0 + tok) * H + h;
         if (splits == 1) {
+            if (sinks != nullptr && lt > 0.f) lt += expf(sinks[h] - m[e]);       // the sink joins the denominator once
             const float inv = lt > 0.f ? 1.f / lt : 0.f;
 #pragma unroll
             for (int nt = 0; nt < NTW; ++nt)
@@ -469,7 +479,7 @@ __global__ void __launch_bounds__(128) latent_attention_wide_kernel(
         long q_rot_head, const __nv_bfloat16* __restrict__ c_cache, const __nv_bfloat16* __restrict__ kr_cache,
         const int* __restrict__ block_table, int table_width, const int* __restrict__ token_req,
         const int* __restrict__ positions, const int* __restrict__ blocks, __nv_bfloat16* __restrict__ out,
-        int H, int rank, int rot, int page_size, float scale, int window) {
+        int H, int rank, int rot, int page_size, float scale, int window, const float* __restrict__ sinks) {
     typedef __nv_bfloat16 bf;
     constexpr int RT = 4 / CH, ROWS = RT * 16;
     extern __shared__ __align__(16) unsigned char raw[];
@@ -630,6 +640,7 @@ __global__ void __launch_bounds__(128) latent_attention_wide_kernel(
         const int r = rt * 16 + g + 8 * e, tok = row_token(r);
         if (tok < 0) continue;
         const size_t row = (size_t)(t0 + tok) * H + row_head(r);
+        if (sinks != nullptr && l[e] > 0.f) l[e] += expf(sinks[row_head(r)] - m[e]);
         const float inv = l[e] > 0.f ? 1.f / l[e] : 0.f;
 #pragma unroll
         for (int nt = 0; nt < NTW; ++nt)
@@ -649,7 +660,8 @@ extern "C" int lb_latent_wide_tokens(int H, int rows) {
 extern "C" int lb_latent_attention_wide(const void* qa, long qa_row, long qa_head, const void* q_rot, long q_rot_row, long q_rot_head,
                                         const void* c_cache, const void* kr_cache, const int* block_table, int table_width,
                                         const int* token_req, const int* positions, const int* blocks, int num_blocks, void* out,
-                                        int H, int rank, int rot, int page_size, float scale, int window, int rows, void* stream) {
+                                        int H, int rank, int rot, int page_size, float scale, int window, int rows, const float* sinks,
+                                        void* stream) {
     if (num_blocks <= 0) return kOk;
     if (H <= 0 || rank <= 0 || rank % 32 || rot < 0 || rot % 16 || page_size <= 0 || window < 0) return kBadSize;
     if ((rows != 32 && rows != 64) || (rows == 64 && rank > 256)) return kBadSize;
@@ -662,7 +674,7 @@ extern "C" int lb_latent_attention_wide(const void* qa, long qa_row, long qa_hea
 #define LB_LW(NTW_, CH_) { static size_t have = 0; ensure_dynamic_smem(latent_attention_wide_kernel<NTW_, CH_>, smem, have); \
         latent_attention_wide_kernel<NTW_, CH_><<<grid, 128, smem, st>>>((const bf*)qa, qa_row, qa_head, (const bf*)q_rot, q_rot_row, \
             q_rot_head, (const bf*)c_cache, (const bf*)kr_cache, block_table, table_width, token_req, positions, blocks, (bf*)out, \
-            H, rank, rot, page_size, scale, window); }
+            H, rank, rot, page_size, scale, window, sinks); }
     if (rows == 64) { if (rank <= 128) LB_LW(16, 1) else LB_LW(32, 1) }
     else { if (rank <= 256) LB_LW(16, 2) else LB_LW(32, 2) }
 #undef LB_LW
@@ -671,13 +683,14 @@ extern "C" int lb_latent_attention_wide(const void* qa, long qa_row, long qa_hea
 
 // grid (listed token blocks' rows): one CTA per (token, head) row of the step
 __global__ void latent_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                    __nv_bfloat16* __restrict__ out, int rank, int splits) {
+                                    __nv_bfloat16* __restrict__ out, int rank, int splits, const float* __restrict__ sinks, int H) {
     const size_t row = blockIdx.x;
     float M = -INFINITY;
     for (int s = 0; s < splits; ++s) M = fmaxf(M, part_ml[(row * splits + s) * 2]);
     if (M == -INFINITY) return;                              // a row that no block of this step owns
     float L = 0.f;
     for (int s = 0; s < splits; ++s) L += part_ml[(row * splits + s) * 2 + 1] * expf(part_ml[(row * splits + s) * 2] - M);
+    if (sinks != nullptr) L += expf(sinks[row % H] - M);       // the sink joins the denominator once, here
     for (int c = threadIdx.x; c < rank; c += blockDim.x) {
         float a = 0.f;
         for (int s = 0; s < splits; ++s) {
@@ -696,7 +709,7 @@ extern "C" int lb_latent_attention_mma(const void* qa, long qa_row, long qa_head
                                        const void* kr_cache, const int* block_table, int table_width, const int* token_req,
                                        const int* positions, const int* blocks, int num_blocks, void* out, float* part_o,
                                        float* part_ml, int tokens, int H, int rank, int rot, int page_size, float scale,
-                                       int window, int splits, void* stream) {
+                                       int window, int splits, const float* sinks, void* stream) {
     if (num_blocks <= 0) return kOk;
     if (H <= 0 || rank <= 0 || rank % 32 || rot < 0 || rot % 16 || page_size <= 0 || window < 0 || splits < 1) return kBadSize;
     if (rank > 512 || splits > 65535) return kTooLarge;
@@ -708,11 +721,11 @@ extern "C" int lb_latent_attention_mma(const void* qa, long qa_row, long qa_head
 #define LB_LA(NTW_) { static size_t have = 0; ensure_dynamic_smem(latent_attention_mma_kernel<NTW_>, smem, have); \
         latent_attention_mma_kernel<NTW_><<<grid, 128, smem, st>>>((const bf*)qa, qa_row, qa_head, (const bf*)q_rot, q_rot_row, q_rot_head, \
             (const bf*)c_cache, (const bf*)kr_cache, block_table, table_width, token_req, positions, blocks, (bf*)out, part_o, \
-            part_ml, H, rank, rot, page_size, scale, window, splits); }
+            part_ml, H, rank, rot, page_size, scale, window, splits, sinks); }
     if (rank <= 128) LB_LA(4) else if (rank <= 256) LB_LA(8) else LB_LA(16)
 #undef LB_LA
     int rc = launch_status();
     if (rc != 0 || splits == 1) return rc;
-    latent_merge_kernel<<<tokens * H, 128, 0, st>>>(part_o, part_ml, (bf*)out, rank, splits);
+    latent_merge_kernel<<<tokens * H, 128, 0, st>>>(part_o, part_ml, (bf*)out, rank, splits, sinks, H);
     return launch_status();
 }

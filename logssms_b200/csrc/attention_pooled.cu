@@ -876,3 +876,92 @@ extern "C" int lb_pooled_attention_tile(const void* q, const void* k_cache, cons
                                                                             (__nv_bfloat16*)out, Hq, vdim, splits, sinks);
     return launch_status();
 }
+
+// ------------------------------------------------------------------------------------------------------------------
+// Queries and keys that are normed over the WHOLE projection (all heads of a token at once), then rotated; the values
+// are the keys as they came in (before norm and rotation).
+//
+//   rownorm_prepare : per token, from qk = [q (Hq * dim) | k (Hkv * dim)]:
+//                       q~ = q / sqrt(mean_all(q^2) + eps) * wq        (wq: a weight per column of the whole row)
+//                       k~ = k / sqrt(mean_all(k^2) + eps) * wk
+//                       q_out = R_p(q~),  k_cache[slot] = R_p(k~),  v_cache[slot] = k
+//                     R_p turns neighbouring pairs (2i, 2i + 1) of the first `rot` columns of every head by the token's
+//                     row of the table (cos | sin of rot / 2 pairs).  Norms and rotation are 32-bit.
+//   head_gate       : o[t, h, :] *= sigmoid(g[t, h])                   (one gate per token and head, in place)
+template <typename T>
+__global__ void __launch_bounds__(256) rownorm_prepare_kernel(const T* __restrict__ qk, long row_stride, const int* __restrict__ positions,
+                                                              const int* __restrict__ slot_mapping, const float* __restrict__ table, int rot,
+                                                              int table_rows, const float* __restrict__ wq, const float* __restrict__ wk,
+                                                              float eps, T* __restrict__ q_out, T* __restrict__ k_cache,
+                                                              T* __restrict__ v_cache, int Hq, int Hkv, int dim, int write_kv) {
+    __shared__ float red[32];
+    const size_t t = blockIdx.x;
+    const T* row = qk + t * row_stride;
+    const int nq = Hq * dim, nk = Hkv * dim;
+    float sq = 0.f, sk = 0.f;
+    for (int c = threadIdx.x; c < nq; c += blockDim.x) { const float v = to_f32(row[c]); sq += v * v; }
+    for (int c = threadIdx.x; c < nk; c += blockDim.x) { const float v = to_f32(row[nq + c]); sk += v * v; }
+    const float inv_q = 1.f / sqrtf(block_sum(sq, red) / (float)nq + eps);
+    const float inv_k = 1.f / sqrtf(block_sum(sk, red) / (float)nk + eps);
+    const int pos = min(max(positions[t], 0), table_rows - 1);
+    const float* cs = table + (size_t)pos * rot;
+    const int half = rot >> 1;
+    const long slot = write_kv ? (long)slot_mapping[t] : -1;
+    for (int c = threadIdx.x; c < nq + nk; c += blockDim.x) {
+        const bool is_q = c < nq;
+        const int cc = is_q ? c : c - nq;                    // column of the whole q (or k) row
+        const int d = cc % dim;                              // column of its head
+        const float* w = is_q ? wq : wk;
+        const float inv = is_q ? inv_q : inv_k;
+        const T* src = row + (is_q ? 0 : nq);
+        const float raw = to_f32(src[cc]);
+        float val = raw * inv * w[cc];
+        if (d < rot) {
+            const float partner = to_f32(src[cc ^ 1]) * inv * w[cc ^ 1];
+            const float co = cs[d >> 1], si = cs[half + (d >> 1)];
+            val = (d & 1) ? val * co + partner * si : val * co - partner * si;
+        }
+        if (is_q) q_out[t * nq + cc] = from_f32<T>(val);
+        else if (slot >= 0) {
+            k_cache[(size_t)slot * nk + cc] = from_f32<T>(val);
+            v_cache[(size_t)slot * nk + cc] = src[cc];
+        }
+    }
+}
+
+// qk: [tokens, (Hq + Hkv) * dim] (column view allowed); table: float32 [table_rows, rot]; wq: float32 [Hq * dim];
+// wk: float32 [Hkv * dim]; q_out: [tokens, Hq, dim]; caches: [slots, Hkv, dim], both
+extern "C" int lb_rownorm_prepare(const void* qk, long row_stride, const int* positions, const int* slot_mapping, const float* table,
+                                  int rot, int table_rows, const float* wq, const float* wk, float eps, void* q_out, void* k_cache,
+                                  void* v_cache, int tokens, int Hq, int Hkv, int dim, int write_kv, int dtype, void* stream) {
+    if (tokens <= 0) return kOk;
+    if (Hq <= 0 || Hkv <= 0 || dim <= 0 || rot < 0 || rot > dim || (rot & 1) || table_rows <= 0) return kBadSize;
+    LB_DISPATCH_DTYPE(dtype, rownorm_prepare_kernel<T><<<tokens, 256, 0, (cudaStream_t)stream>>>(
+        (const T*)qk, row_stride, positions, slot_mapping, table, rot, table_rows, wq, wk, eps, (T*)q_out, (T*)k_cache, (T*)v_cache,
+        Hq, Hkv, dim, write_kv));
+    return launch_status();
+}
+
+template <typename T, typename TG>
+__global__ void head_gate_kernel(T* __restrict__ o, const TG* __restrict__ g, long g_stride, int H, int width, long total) {
+    const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const long t = i / ((long)H * width);
+    const int h = (int)((i / width) % H);
+    const float gate = 1.f / (1.f + expf(-to_f32(g[t * g_stride + h])));
+    o[i] = from_f32<T>(to_f32(o[i]) * gate);
+}
+
+// o: contiguous [tokens, H, width], scaled in place; g: [tokens, >= H] gate logits (float32 with `g_f32`, else o's dtype; row
+// stride in elements)
+extern "C" int lb_head_gate(void* o, const void* g, long g_stride, int g_f32, int tokens, int H, int width, int dtype, void* stream) {
+    if (tokens <= 0) return kOk;
+    if (H <= 0 || width <= 0) return kBadSize;
+    const long total = (long)tokens * H * width;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    LB_DISPATCH_DTYPE(dtype, {
+        if (g_f32) head_gate_kernel<T, float><<<blocks, 256, 0, (cudaStream_t)stream>>>((T*)o, (const float*)g, g_stride, H, width, total);
+        else head_gate_kernel<T, T><<<blocks, 256, 0, (cudaStream_t)stream>>>((T*)o, (const T*)g, g_stride, H, width, total);
+    });
+    return launch_status();
+}

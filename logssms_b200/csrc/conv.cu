@@ -3,7 +3,7 @@
 //   u_t[ch]  = round(xBC_t[ch] * region_scale(ch))                (three regions: x | B | C)
 //   c_t[ch]  = sum_{j<K} w[ch, j] * u_{t-(K-1)+j}[ch] (+ bias[ch])  ; inputs before the portion come
 //              from the request's conv state (zeros when the request starts at position 0)
-//   out_t    = round(silu(round(c_t)))
+//   out_t    = round(silu(round(c_t)))                            (`act` 1: out_t = round(c_t), no activation)
 //   state'   = the last K-1 scaled inputs u, oldest first
 // (python/logssms/kernel/linear_attention/packed_conv.py:96-140; decode form
 // python/logssms/kernel/linear_attention/conv_decode.py:112-278.)
@@ -26,6 +26,7 @@ struct ConvArgs {
     void* out;                             // [tokens, C] contiguous
     const int* cu_seqlens; const int* start_pos; const int* slots;
     int C; int end0; int end1; float s0; float s1; float s2;
+    int act;                               // what follows the convolution: 0 silu, 1 nothing
 };
 
 template <typename T>
@@ -61,7 +62,7 @@ __global__ void conv_forward_kernel(ConvArgs a) {
 #pragma unroll
         for (int j = 0; j < K; ++j) acc += win[j] * w[j];
         acc = round_to<T>(acc + bias);
-        ((T*)a.out)[(size_t)(begin + t) * a.C + c] = from_f32<T>(silu_f(acc));
+        ((T*)a.out)[(size_t)(begin + t) * a.C + c] = from_f32<T>(a.act == 0 ? silu_f(acc) : acc);
 #pragma unroll
         for (int j = 0; j < K - 1; ++j) win[j] = win[j + 1];
     }
@@ -176,7 +177,7 @@ __global__ void __launch_bounds__(128) conv_forward_vec_kernel(ConvArgs a) {
 #pragma unroll
                 for (int j = 0; j < K; ++j) acc += win[e][j] * w[e][j];
                 acc = round_to<T>(acc + bias[e]);
-                acc = silu_fast(acc);                            // the result is rounded to bfloat16 next
+                if (a.act == 0) acc = silu_fast(acc);                            // the result is rounded to bfloat16 next
                 if (e & 1) o[e >> 1].y = __float2bfloat16_rn(acc); else o[e >> 1].x = __float2bfloat16_rn(acc);
 #pragma unroll
                 for (int j = 0; j < K - 1; ++j) win[e][j] = win[e][j + 1];
@@ -295,7 +296,7 @@ __global__ void __launch_bounds__(kTileThreads, 3) conv_forward_tile_kernel(Conv
 #pragma unroll
             for (int j = 0; j < K; ++j) acc += win[e][j] * w[e][j];
             acc = round_to<T>(acc + bias[e]);
-            acc = silu_fast(acc);                            // the result is rounded to bfloat16 next
+            if (a.act == 0) acc = silu_fast(acc);                            // the result is rounded to bfloat16 next
             if (e & 1) o[e >> 1].y = __float2bfloat16_rn(acc); else o[e >> 1].x = __float2bfloat16_rn(acc);
 #pragma unroll
             for (int j = 0; j < K - 1; ++j) win[e][j] = win[e][j + 1];
@@ -340,7 +341,7 @@ int launch(const ConvArgs& a, int B, int K, int max_len, cudaStream_t s) {
         }                                                                     \
         break;
     switch (K) {
-        LB_CONV_K(2) LB_CONV_K(3) LB_CONV_K(4) LB_CONV_K(5) LB_CONV_K(6) LB_CONV_K(7) LB_CONV_K(8)
+        LB_CONV_K(1) LB_CONV_K(2) LB_CONV_K(3) LB_CONV_K(4) LB_CONV_K(5) LB_CONV_K(6) LB_CONV_K(7) LB_CONV_K(8)
         default: return kBadSize;
     }
 #undef LB_CONV_K
@@ -351,11 +352,11 @@ int launch(const ConvArgs& a, int B, int K, int max_len, cudaStream_t s) {
 extern "C" int lb_causal_conv1d(const void* x, long x_stride, const float* weight, const float* bias, void* state,
                                 void* out, const int* cu_seqlens, const int* start_pos, const int* slots, int B,
                                 int max_len, int C, int K, int end0, int end1, float s0, float s1, float s2,
-                                int dtype, void* stream) {
+                                int act, int dtype, void* stream) {
     if (B <= 0 || max_len <= 0) return kOk;
-    if (C <= 0 || K < 2 || K > 8) return kBadSize;
-    ConvArgs a{x, x_stride, weight, bias, state, out, cu_seqlens, start_pos, slots, C, end0, end1, s0, s1, s2};
-    if (vec_ok(a, dtype) && K <= 5) {
+    if (C <= 0 || K < 1 || K > 8 || act < 0 || act > 1) return kBadSize;
+    ConvArgs a{x, x_stride, weight, bias, state, out, cu_seqlens, start_pos, slots, C, end0, end1, s0, s1, s2, act};
+    if (vec_ok(a, dtype) && K >= 2 && K <= 5) {
         switch (K) {
             case 2: launch_vec<2>(a, B, max_len, (cudaStream_t)stream); break;
             case 3: launch_vec<3>(a, B, max_len, (cudaStream_t)stream); break;

@@ -43,7 +43,7 @@ __global__ void delta_scan_kernel(const T* __restrict__ q, const T* __restrict__
                                   const float* __restrict__ z, const float* __restrict__ dt_bias, const float* __restrict__ A_log,
                                   const TB* __restrict__ beta, long beta_stride, float* __restrict__ o, float* state,
                                   const int* __restrict__ cu, const int* __restrict__ start_pos, const int* __restrict__ slots,
-                                  const int* __restrict__ request_list, int H, int Hk, int dim, int vdim, float q_scale, float unit_eps) {
+                                  const int* __restrict__ request_list, int H, int Hk, int dim, int vdim, float q_scale, float unit_eps, int zdim) {
     constexpr int DP = R * DS;                       // key channels, padded
     extern __shared__ float sm[];
     const int cols = blockDim.x / DS;
@@ -95,7 +95,8 @@ __global__ void delta_scan_kernel(const T* __restrict__ q, const T* __restrict__
         }
         for (int i = threadIdx.x; i < n * DP; i += blockDim.x) {
             const int tt = i / DP, d = i % DP;
-            gs[i] = d < dim ? expf(-rate * softplus_f(z[((size_t)(t0 + tt) * H + h) * dim + d] + dt_bias[h * dim + d])) : 0.f;
+            const int zc = zdim == 1 ? 0 : d;           // one decay per head: every key channel reads the same column
+            gs[i] = d < dim ? expf(-rate * softplus_f(z[((size_t)(t0 + tt) * H + h) * zdim + zc] + dt_bias[h * zdim + zc])) : 0.f;
         }
         for (int i = threadIdx.x; i < n * cols; i += blockDim.x) {
             const int tt = i / cols, cc = blockIdx.x * cols + i % cols;
@@ -135,7 +136,7 @@ template <typename T, typename TB, int R, int DS>
 static int launch_delta_scan(const void* q, const void* k, const void* v, long row_stride, const float* z, const float* dt_bias,
                              const float* A_log, const void* beta, long beta_stride, float* o, float* state, const int* cu,
                              const int* start_pos, const int* slots, const int* request_list, int num_requests, int H, int Hk,
-                             int dim, int vdim, float q_scale, float unit_eps, cudaStream_t stream) {
+                             int dim, int vdim, float q_scale, float unit_eps, int zdim, cudaStream_t stream) {
     // few requests: narrow tiles, so that more CTAs share the work
     const int want = (num_requests * H * ((vdim * DS + 127) / 128) < 148) ? 32 : 128;
     const int threads = min(want, (vdim * DS + 31) / 32 * 32);
@@ -146,7 +147,7 @@ static int launch_delta_scan(const void* q, const void* k, const void* v, long r
     ensure_dynamic_smem(delta_scan_kernel<T, TB, R, DS>, smem, have);
     delta_scan_kernel<T, TB, R, DS><<<grid, threads, smem, stream>>>((const T*)q, (const T*)k, (const T*)v, row_stride, z, dt_bias, A_log,
                                                                      (const TB*)beta, beta_stride, o, state, cu, start_pos, slots,
-                                                                     request_list, H, Hk, dim, vdim, q_scale, unit_eps);
+                                                                     request_list, H, Hk, dim, vdim, q_scale, unit_eps, zdim);
     return launch_status();
 }
 
@@ -168,7 +169,7 @@ template <typename T, typename TB>
 __global__ void delta_prepare_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, long row_stride,
                                      const float* __restrict__ z, const float* __restrict__ dt_bias, const float* __restrict__ A_log,
                                      const TB* __restrict__ beta, long beta_stride, float* __restrict__ prepared, float* __restrict__ values,
-                                     long pairs, int H, int Hk, int dim, int vdim, int DP, float q_scale, float unit_eps) {
+                                     long pairs, int H, int Hk, int dim, int vdim, int DP, float q_scale, float unit_eps, int zdim) {
     const int lane = threadIdx.x & 31;
     const long pair = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (pair >= pairs) return;
@@ -184,12 +185,13 @@ __global__ void delta_prepare_kernel(const T* __restrict__ q, const T* __restric
     qq = warp_sum(qq); kk = warp_sum(kk); qk = warp_sum(qk);
     const float qn = q_scale / sqrtf(qq + unit_eps), kn = 1.f / sqrtf(kk + unit_eps), rate = expf(A_log[h]);
     float* row = prepared + (size_t)pair * (3 * DP + 4);
-    const float* zr = z + ((size_t)t * H + h) * dim;
+    const float* zr = z + ((size_t)t * H + h) * zdim;
     for (int d = lane; d < DP; d += 32) {
         const bool in = d < dim;
         row[d] = in ? to_f32(qr[d]) * qn : 0.f;
         row[DP + d] = in ? to_f32(kr[d]) * kn : 0.f;
-        row[2 * DP + d] = in ? expf(-rate * softplus_f(zr[d] + dt_bias[h * dim + d])) : 0.f;
+        const int zc = zdim == 1 ? 0 : d;
+        row[2 * DP + d] = in ? expf(-rate * softplus_f(zr[zc] + dt_bias[h * zdim + zc])) : 0.f;
     }
     if (lane < 4) {
         float x = 0.f;
@@ -312,9 +314,9 @@ extern "C" int lb_delta_scan_rows(const void* q, const void* k, const void* v, l
                                   const float* A_log, const void* beta, long beta_stride, int beta_f32, float* prepared, float* values, float* o,
                                   float* state, const int* cu, const int* start_pos, const int* slots, const int* request_list,
                                   int num_requests, long tokens, int H, int Hk, int dim, int vdim, float q_scale, float unit_eps,
-                                  int rows, int dtype, void* stream) {
+                                  int rows, int zdim, int dtype, void* stream) {
     if (num_requests <= 0 || tokens <= 0) return kOk;
-    if (H <= 0 || Hk <= 0 || H % Hk || dim <= 0 || vdim <= 0 || H > 65535 || num_requests > 65535) return kBadSize;
+    if (H <= 0 || Hk <= 0 || H % Hk || dim <= 0 || vdim <= 0 || H > 65535 || num_requests > 65535 || (zdim != dim && zdim != 1)) return kBadSize;
     if (dim > 512) return kTooLarge;
     cudaStream_t st = (cudaStream_t)stream;
     int DP = kMinPadded;
@@ -326,7 +328,7 @@ extern "C" int lb_delta_scan_rows(const void* q, const void* k, const void* v, l
     const int warps = 4;
     const unsigned blocks = (unsigned)((pairs + warps - 1) / warps);
 #define LB_PREPARE(TB_) delta_prepare_kernel<T, TB_><<<blocks, warps * 32, 0, st>>>((const T*)q, (const T*)k, (const T*)v, row_stride, z, \
-        dt_bias, A_log, (const TB_*)beta, beta_stride, prepared, values, pairs, H, Hk, dim, vdim, DP, q_scale, unit_eps)
+        dt_bias, A_log, (const TB_*)beta, beta_stride, prepared, values, pairs, H, Hk, dim, vdim, DP, q_scale, unit_eps, zdim)
     LB_DISPATCH_DTYPE(dtype, { if (beta_f32) LB_PREPARE(float); else LB_PREPARE(T); });
 #undef LB_PREPARE
     const int status = launch_status();
@@ -370,7 +372,7 @@ __global__ void __launch_bounds__(128) delta_chunk_prepare_kernel(
         const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, long row_stride, const float* __restrict__ z,
         const float* __restrict__ dt_bias, const float* __restrict__ A_log, const TB* __restrict__ beta, long beta_stride,
         const int* __restrict__ cu, const int* __restrict__ chunks, float* __restrict__ records, float* __restrict__ values,
-        int H, int Hk, int dim, int vdim, int DP, float q_scale, float unit_eps) {
+        int H, int Hk, int dim, int vdim, int DP, float q_scale, float unit_eps, int zdim) {
     constexpr int C = kDeltaChunk;
     extern __shared__ float sm[];
     float* L = sm;                                   // [C][DP] log-decays, then their running sums
@@ -406,7 +408,8 @@ __global__ void __launch_bounds__(128) delta_chunk_prepare_kernel(
     const float rate = expf(A_log[h]);
     for (int i = threadIdx.x; i < C * DP; i += blockDim.x) {
         const int j = i / DP, d = i % DP;
-        L[i] = (j < n && d < dim) ? -rate * softplus_f(z[((size_t)(t0 + j) * H + h) * dim + d] + dt_bias[h * dim + d]) : 0.f;
+        const int zc = zdim == 1 ? 0 : d;
+        L[i] = (j < n && d < dim) ? -rate * softplus_f(z[((size_t)(t0 + j) * H + h) * zdim + zc] + dt_bias[h * zdim + zc]) : 0.f;
     }
     __syncthreads();
     for (int d = threadIdx.x; d < DP; d += blockDim.x) {
@@ -596,9 +599,9 @@ extern "C" int lb_delta_scan_chunks(const void* q, const void* k, const void* v,
                                     const float* A_log, const void* beta, long beta_stride, int beta_f32, float* records, float* values,
                                     float* o, float* state, const int* cu, const int* start_pos, const int* slots, const int* chunks,
                                     int num_chunks, const int* per_request, int num_long, int H, int Hk, int dim, int vdim, float q_scale,
-                                    float unit_eps, int rows, int dtype, void* stream) {
+                                    float unit_eps, int rows, int zdim, int dtype, void* stream) {
     if (num_chunks <= 0 || num_long <= 0) return kOk;
-    if (H <= 0 || Hk <= 0 || H % Hk || dim <= 0 || vdim <= 0 || H > 65535 || num_long > 65535) return kBadSize;
+    if (H <= 0 || Hk <= 0 || H % Hk || dim <= 0 || vdim <= 0 || H > 65535 || num_long > 65535 || (zdim != dim && zdim != 1)) return kBadSize;
     if (dim > 256) return kTooLarge;
     cudaStream_t st = (cudaStream_t)stream;
     int DP = 64;                                     // a column is shared by 16 or 32 lanes of 4 or 8 rows each
@@ -606,7 +609,7 @@ extern "C" int lb_delta_scan_chunks(const void* q, const void* k, const void* v,
     const size_t smem = (size_t)(3 * kDeltaChunk * DP + kDeltaChunk) * sizeof(float);
     dim3 grid(num_chunks, H);
 #define LB_PREPARE(TB_) delta_chunk_prepare_kernel<T, TB_><<<grid, 128, smem, st>>>((const T*)q, (const T*)k, (const T*)v, row_stride, z, \
-        dt_bias, A_log, (const TB_*)beta, beta_stride, cu, chunks, records, values, H, Hk, dim, vdim, DP, q_scale, unit_eps)
+        dt_bias, A_log, (const TB_*)beta, beta_stride, cu, chunks, records, values, H, Hk, dim, vdim, DP, q_scale, unit_eps, zdim)
     LB_DISPATCH_DTYPE(dtype, { if (beta_f32) LB_PREPARE(float); else LB_PREPARE(T); });
 #undef LB_PREPARE
     const int status = launch_status();
@@ -623,19 +626,19 @@ extern "C" int lb_delta_scan_chunks(const void* q, const void* k, const void* v,
 }
 
 // q, k: [tokens, Hk*dim] and v: [tokens, H*vdim], column views of one buffer (common row stride, in elements);
-// z: float32 [tokens, H*dim]; dt_bias: float32 [H*dim]; A_log: float32 [H]; beta: [tokens, >= H] logits of the write's
+// z: float32 [tokens, H*zdim]; dt_bias: float32 [H*zdim] with zdim = dim (a decay per key channel) or 1 (one per head); A_log: float32 [H]; beta: [tokens, >= H] logits of the write's
 // gate (float32 with `beta_f32`, else the activation dtype; row stride in elements); o: float32 [tokens, H*vdim];
 // state: float32 [slots, H, dim, vdim].
 extern "C" int lb_delta_scan(const void* q, const void* k, const void* v, long row_stride, const float* z, const float* dt_bias,
                              const float* A_log, const void* beta, long beta_stride, int beta_f32, float* o, float* state,
                              const int* cu, const int* start_pos, const int* slots, const int* request_list, int num_requests,
-                             int H, int Hk, int dim, int vdim, float q_scale, float unit_eps, int dtype, void* stream) {
+                             int H, int Hk, int dim, int vdim, float q_scale, float unit_eps, int zdim, int dtype, void* stream) {
     if (num_requests <= 0) return kOk;
-    if (H <= 0 || Hk <= 0 || H % Hk || dim <= 0 || vdim <= 0 || H > 65535) return kBadSize;
+    if (H <= 0 || Hk <= 0 || H % Hk || dim <= 0 || vdim <= 0 || H > 65535 || (zdim != dim && zdim != 1)) return kBadSize;
     if (dim > 512) return kTooLarge;
     cudaStream_t st = (cudaStream_t)stream;
 #define LB_DELTA_B(TB_, R_, DS_) return (launch_delta_scan<T, TB_, R_, DS_>(q, k, v, row_stride, z, dt_bias, A_log, beta, beta_stride, o, \
-        state, cu, start_pos, slots, request_list, num_requests, H, Hk, dim, vdim, q_scale, unit_eps, st))
+        state, cu, start_pos, slots, request_list, num_requests, H, Hk, dim, vdim, q_scale, unit_eps, zdim, st))
 #define LB_DELTA(R_, DS_) LB_DISPATCH_DTYPE(dtype, { if (beta_f32) LB_DELTA_B(float, R_, DS_); else LB_DELTA_B(T, R_, DS_); })
     if (dim <= 16) { LB_DELTA(16, 1); }
     else if (dim <= 32) { LB_DELTA(32, 1); }

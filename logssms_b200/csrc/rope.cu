@@ -8,20 +8,21 @@
 #include "lb200/common.cuh"
 using namespace lb200;
 
-__global__ void rope_table_kernel(float* __restrict__ table, const float* __restrict__ inv_freq, int rows, int half) {
+__global__ void rope_table_kernel(float* __restrict__ table, const float* __restrict__ inv_freq, int rows, int half, float magnitude) {
     const int p = blockIdx.x;
     for (int i = threadIdx.x; i < half; i += blockDim.x) {
         const float angle = (float)p * inv_freq[i];
         float s, c;
         sincosf(angle, &s, &c);
-        table[(size_t)p * 2 * half + i] = c;
-        table[(size_t)p * 2 * half + half + i] = s;
+        table[(size_t)p * 2 * half + i] = c * magnitude;
+        table[(size_t)p * 2 * half + half + i] = s * magnitude;
     }
 }
 
-extern "C" int lb_rope_table(float* table, const float* inv_freq, int rows, int half, void* stream) {
+// `magnitude` multiplies every cos and sin (1: a plain rotation)
+extern "C" int lb_rope_table(float* table, const float* inv_freq, int rows, int half, float magnitude, void* stream) {
     if (rows <= 0 || half <= 0) return kBadSize;
-    rope_table_kernel<<<rows, 64, 0, (cudaStream_t)stream>>>(table, inv_freq, rows, half);
+    rope_table_kernel<<<rows, 64, 0, (cudaStream_t)stream>>>(table, inv_freq, rows, half, magnitude);
     return launch_status();
 }
 

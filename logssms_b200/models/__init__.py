@@ -45,4 +45,8 @@ from ..config.pupopel import ARCHITECTURE as _PUPOPEL, PupopelConfig  # noqa: E4
 
 register_architecture(_PUPOPEL, PupopelConfig)
 
+from ..config.zarisun import ARCHITECTURE as _ZARISUN, ZarisunConfig  # noqa: E402
+
+register_architecture(_ZARISUN, ZarisunConfig)
+
 __all__ = ["Architecture", "DecoderModel", "build_model", "register_architecture"]

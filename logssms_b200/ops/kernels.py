@@ -188,14 +188,14 @@ def scale(x: torch.Tensor, s: float, to_f32: bool = False) -> torch.Tensor:
 
 
 # --------------------------------------------------------------------------- rotary + cache store
-def rope_table(inv_freq: torch.Tensor, rows: int) -> torch.Tensor:
-    """[rows, 2*half] float32: cos | sin of position * inv_freq."""
+def rope_table(inv_freq: torch.Tensor, rows: int, magnitude: float = 1.0) -> torch.Tensor:
+    """[rows, 2*half] float32: cos | sin of position * inv_freq, both times `magnitude`."""
     _cuda(inv_freq)
     _need(inv_freq.dtype == torch.float32 and inv_freq.is_contiguous(), "inv_freq must be contiguous float32")
     half = inv_freq.numel()
     table = torch.empty((rows, 2 * half), dtype=torch.float32, device=inv_freq.device)
-    f = _fn("rope", "lb_rope_table", [c_void_p, c_void_p, c_int, c_int, c_void_p])
-    _check(f(_ptr(table), _ptr(inv_freq), rows, half, _stream()), "rope_table")
+    f = _fn("rope", "lb_rope_table", [c_void_p, c_void_p, c_int, c_int, c_float, c_void_p])
+    _check(f(_ptr(table), _ptr(inv_freq), rows, half, magnitude, _stream()), "rope_table")
     return table
 
 
@@ -520,27 +520,31 @@ def attention_prefill_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
 # --------------------------------------------------------------------------- Mamba2
 def causal_conv1d(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, state: torch.Tensor,
                   cu_seqlens: torch.Tensor, start_pos: torch.Tensor, slots: torch.Tensor, num_requests: int,
-                  max_len: int, region_ends: tuple[int, int], region_scales: tuple[float, float, float]) -> torch.Tensor:
+                  max_len: int, region_ends: tuple[int, int], region_scales: tuple[float, float, float],
+                  activation: str = "silu") -> torch.Tensor:
     """x: [tokens, C] (column view allowed); weight: [C, K] float32; state: [slots, C, K-1] of x's dtype,
-    read then rewritten in place.  Returns silu(conv) as a contiguous [tokens, C]."""
+    read then rewritten in place (None with one tap: nothing is carried).  Returns silu(conv), or with `activation`
+    "none" conv itself, as a contiguous [tokens, C]."""
     _cuda(x, weight, bias, state, cu_seqlens, start_pos, slots)
     tokens, C = x.shape
     K = weight.shape[1]
     _need(x.stride(1) == 1, "conv input needs unit column stride")
     _need(weight.dtype == torch.float32 and weight.shape == (C, K) and weight.is_contiguous(), "conv weight must be float32 [C, K]")
     _need(bias is None or (bias.dtype == torch.float32 and bias.shape == (C,) and bias.is_contiguous()), "conv bias must be float32 [C]")
-    _need(2 <= K <= 8, f"conv kernel sizes 2..8 are built, got {K}")
-    _need(state.dtype == x.dtype and state.is_contiguous() and state.shape[1:] == (C, K - 1),
+    _need(1 <= K <= 8, f"conv kernel sizes 1..8 are built, got {K}")
+    _need(activation in ("silu", "none"), "the convolution is followed by silu or by nothing")
+    _need((K == 1 and state is None) or (state is not None and state.dtype == x.dtype and state.is_contiguous()
+                                         and state.shape[1:] == (C, K - 1)),
           "conv state must be contiguous [slots, C, K-1] of the activation dtype")
     for t, n in ((cu_seqlens, "cu_seqlens"), (start_pos, "start_pos"), (slots, "slots")):
         _i32(t, n)
     out = torch.empty((tokens, C), dtype=x.dtype, device=x.device)
     f = _fn("conv", "lb_causal_conv1d", [c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                          c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float,
-                                         c_float, c_int, c_void_p])
+                                         c_float, c_int, c_int, c_void_p])
     _check(f(_ptr(x), x.stride(0), _ptr(weight), _ptr(bias), _ptr(state), _ptr(out), _ptr(cu_seqlens),
              _ptr(start_pos), _ptr(slots), num_requests, max_len, C, K, region_ends[0], region_ends[1],
-             region_scales[0], region_scales[1], region_scales[2], _code(x), _stream()), "causal_conv1d",
+             region_scales[0], region_scales[1], region_scales[2], int(activation == "none"), _code(x), _stream()), "causal_conv1d",
            launches=1 if max_len <= 8 else 2)
     return out
 
@@ -1196,25 +1200,29 @@ def gla_norm_gate(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps
 # --------------------------------------------------------------------------- attention over a cache of latents
 def latent_prepare(proj: torch.Tensor, num_heads: int, nope_dim: int, rot_dim: int, rank: int, positions: torch.Tensor,
                    slot_mapping: torch.Tensor, cos_sin: torch.Tensor, norm_weight: torch.Tensor, eps: float,
-                   c_cache: torch.Tensor, kr_cache: torch.Tensor, write_cache: bool = True) -> None:
+                   c_cache: torch.Tensor, kr_cache: torch.Tensor, write_cache: bool = True, neighbours: bool = False) -> None:
     """proj: [tokens, H*(nope+rot) + rank + rot] = queries | down-projection.  Stores the normalised latent and the
-    rotated shared key part at `slot_mapping`, and rotates every head's rotated query part in place."""
+    rotated shared key part at `slot_mapping`, and rotates every head's rotated query part in place.  `neighbours`: the
+    rotation pairs column 2i with 2i + 1 (else i with i + n/2).  Without `write_cache` proj may hold the queries alone
+    (`norm_weight` may then be None): nothing but their rotation happens."""
     _cuda(proj, positions, slot_mapping, cos_sin, norm_weight, c_cache, kr_cache)
     T = proj.shape[0]
     q_cols = num_heads * (nope_dim + rot_dim)
-    _need(proj.dim() == 2 and proj.stride(1) == 1 and proj.shape[1] == q_cols + rank + rot_dim, "proj must hold queries | latent | rotated key")
+    _need(proj.dim() == 2 and proj.stride(1) == 1 and (proj.shape[1] == q_cols + rank + rot_dim or (not write_cache and proj.shape[1] == q_cols)),
+          "proj must hold queries | latent | rotated key")
     _i32(positions, "positions")
     _i32(slot_mapping, "slot_mapping")
     _need(cos_sin.dtype == torch.float32 and cos_sin.dim() == 2 and cos_sin.is_contiguous(), "cos/sin table must be contiguous float32")
-    _need(norm_weight.dtype == torch.float32 and norm_weight.shape == (rank,) and norm_weight.is_contiguous(), "latent norm weight must be float32 [rank]")
+    _need((norm_weight is None and not write_cache) or (norm_weight.dtype == torch.float32 and norm_weight.shape == (rank,)
+                                                        and norm_weight.is_contiguous()), "latent norm weight must be float32 [rank]")
     _need(c_cache.is_contiguous() and kr_cache.is_contiguous() and c_cache.dtype == proj.dtype == kr_cache.dtype
           and c_cache.shape[-1] == rank and kr_cache.shape[-1] == rot_dim, "latent caches must be [..., rank] and [..., rot_dim] of the activation dtype")
     f = _fn("attention_latent", "lb_latent_prepare", [c_void_p, c_long, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
-                                                      c_void_p, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int,
+                                                      c_void_p, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int, c_int,
                                                       c_int, c_void_p])
     _check(f(_ptr(proj), proj.stride(0) if T > 1 else proj.shape[1], q_cols, num_heads, nope_dim, rot_dim, rank, _ptr(positions),
              _ptr(slot_mapping), _ptr(cos_sin), cos_sin.shape[0], cos_sin.shape[1], _ptr(norm_weight), eps, _ptr(c_cache),
-             _ptr(kr_cache), int(write_cache), T, _code(proj), _stream()), "latent_prepare")
+             _ptr(kr_cache), int(write_cache), int(neighbours), T, _code(proj), _stream()), "latent_prepare")
 
 
 def heads_matmul(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
@@ -1241,13 +1249,16 @@ def heads_matmul(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = No
 
 def latent_attention(qa: torch.Tensor, q_rot: torch.Tensor, c_cache: torch.Tensor, kr_cache: torch.Tensor,
                      block_table: torch.Tensor, token_req: torch.Tensor, positions: torch.Tensor, scale: float,
-                     window: int = 0, token_list: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+                     window: int = 0, token_list: torch.Tensor | None = None, out: torch.Tensor | None = None,
+                     sinks: torch.Tensor | None = None) -> torch.Tensor:
     """Softmax attention in the latent space.  qa: [tokens, H, rank] (queries folded through the key expansion);
     q_rot: [tokens, H, rot] (a strided view); caches [pages, page_size, rank] and [pages, page_size, rot].  Token t at
     position p sees keys j of its request with 0 <= p - j < window (0: all).  Returns the weighted sums of the cached
-    latents [tokens, H, rank]; with `token_list` only those rows are written."""
-    _cuda(qa, q_rot, c_cache, kr_cache, block_table, token_req, positions, token_list)
+    latents [tokens, H, rank]; with `token_list` only those rows are written.  `sinks` (float32 [H] or None): exp(sinks[h])
+    joins head h's softmax denominator, with no key and no value."""
+    _cuda(qa, q_rot, c_cache, kr_cache, block_table, token_req, positions, token_list, sinks)
     T, H, rank = qa.shape
+    _latent_sinks(sinks, H)
     rot = kr_cache.shape[-1]
     _need(qa.is_contiguous() and q_rot.shape == (T, H, rot) and (rot == 0 or q_rot.stride(2) == 1) and q_rot.dtype == qa.dtype,
           "q_rot must be [tokens, H, rot] with unit stride in its last axis")
@@ -1264,11 +1275,16 @@ def latent_attention(qa: torch.Tensor, q_rot: torch.Tensor, c_cache: torch.Tenso
         out = torch.empty((T, H, rank), dtype=qa.dtype, device=qa.device)
     f = _fn("attention_latent", "lb_latent_attention", [c_void_p, c_void_p, c_long, c_long, c_void_p, c_void_p, c_void_p, c_int,
                                                         c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
-                                                        c_float, c_int, c_int, c_void_p])
+                                                        c_float, c_int, c_void_p, c_int, c_void_p])
     _check(f(_ptr(qa), _ptr(q_rot), q_rot.stride(0), q_rot.stride(1), _ptr(c_cache), _ptr(kr_cache), _ptr(block_table),
              block_table.shape[1], _ptr(token_req), _ptr(positions), _ptr(token_list), n, _ptr(out), H, rank, rot,
-             c_cache.shape[1], scale, window, _code(qa), _stream()), "latent_attention", f"(rank {rank}, rot {rot})")
+             c_cache.shape[1], scale, window, _ptr(sinks), _code(qa), _stream()), "latent_attention", f"(rank {rank}, rot {rot})")
     return out
+
+
+def _latent_sinks(sinks, num_heads: int) -> None:
+    _need(sinks is None or (sinks.is_cuda and sinks.dtype == torch.float32 and sinks.shape == (num_heads,) and sinks.is_contiguous()),
+          "sinks must be float32 [heads] on the device")
 
 
 LATENT_MMA = os.environ.get("LOGSSMS_B200_LATENT_MMA", "1") != "0"
@@ -1287,12 +1303,13 @@ def latent_splits(num_blocks: int, num_heads: int, keys: int) -> int:
 
 def latent_attention_mma(qa: torch.Tensor, q_rot: torch.Tensor, c_cache: torch.Tensor, kr_cache: torch.Tensor,
                          block_table: torch.Tensor, token_req: torch.Tensor, positions: torch.Tensor, blocks: torch.Tensor | None,
-                         scale: float, window: int = 0, splits: int = 1) -> torch.Tensor:
+                         scale: float, window: int = 0, splits: int = 1, sinks: torch.Tensor | None = None) -> torch.Tensor:
     """`latent_attention` on the tensor cores for all tokens of a step.  `blocks`: int32 [n, 2] (first token row, number
     of tokens) of `StepContext.token_blocks(max(1, 16 // H))`: every token of the step in exactly one block; None: every
     token a block of its own (a step of single tokens needs no list)."""
-    _cuda(qa, q_rot, c_cache, kr_cache, block_table, token_req, positions, blocks)
+    _cuda(qa, q_rot, c_cache, kr_cache, block_table, token_req, positions, blocks, sinks)
     T, H, rank = qa.shape
+    _latent_sinks(sinks, H)
     rot = kr_cache.shape[-1]
     _need(latent_attention_mma_ok(qa, rot), "latent_attention_mma takes bfloat16, rank a multiple of 32 up to 512, rot a multiple of 16")
     _need(qa.stride(2) == 1 and q_rot.shape == (T, H, rot) and (rot == 0 or q_rot.stride(2) == 1) and q_rot.dtype == qa.dtype,
@@ -1310,10 +1327,10 @@ def latent_attention_mma(qa: torch.Tensor, q_rot: torch.Tensor, c_cache: torch.T
         part_ml = torch.empty((T * H, splits, 2), dtype=torch.float32, device=qa.device)
     f = _fn("attention_latent", "lb_latent_attention_mma", [c_void_p, c_long, c_long, c_void_p, c_long, c_long, c_void_p, c_void_p, c_void_p, c_int,
                                                             c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
-                                                            c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p])
+                                                            c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p])
     _check(f(_ptr(qa), qa.stride(0), qa.stride(1), _ptr(q_rot), q_rot.stride(0), q_rot.stride(1), _ptr(c_cache), _ptr(kr_cache), _ptr(block_table),
              block_table.shape[1], _ptr(token_req), _ptr(positions), _ptr(blocks), T if blocks is None else blocks.shape[0], _ptr(out), _ptr(part_o),
-             _ptr(part_ml), T, H, rank, rot, c_cache.shape[1], scale, window, splits, _stream()), "latent_attention_mma",
+             _ptr(part_ml), T, H, rank, rot, c_cache.shape[1], scale, window, splits, _ptr(sinks), _stream()), "latent_attention_mma",
            f"(rank {rank}, rot {rot})", launches=2 if splits > 1 else 1)
     return out
 
@@ -1334,12 +1351,13 @@ def latent_wide_tokens(num_heads: int, rows: int) -> int:
 
 def latent_attention_wide(qa: torch.Tensor, q_rot: torch.Tensor, c_cache: torch.Tensor, kr_cache: torch.Tensor,
                           block_table: torch.Tensor, token_req: torch.Tensor, positions: torch.Tensor, blocks: torch.Tensor,
-                          scale: float, window: int = 0, rows: int = 32) -> torch.Tensor:
+                          scale: float, window: int = 0, rows: int = 32, sinks: torch.Tensor | None = None) -> torch.Tensor:
     """`latent_attention_mma` for steps with prompt portions: a CTA holds `rows` (32 or 64) (token, head) rows of
     neighbouring tokens, so a staged key tile serves more rows, and a warp keeps its rows' weights in registers.
     `blocks`: `StepContext.token_blocks(latent_wide_tokens(H, rows))`."""
-    _cuda(qa, q_rot, c_cache, kr_cache, block_table, token_req, positions, blocks)
+    _cuda(qa, q_rot, c_cache, kr_cache, block_table, token_req, positions, blocks, sinks)
     T, H, rank = qa.shape
+    _latent_sinks(sinks, H)
     rot = kr_cache.shape[-1]
     _need(latent_attention_mma_ok(qa, rot), "latent_attention_wide takes bfloat16, rank a multiple of 32 up to 512, rot a multiple of 16")
     _need(qa.stride(2) == 1 and q_rot.shape == (T, H, rot) and (rot == 0 or q_rot.stride(2) == 1) and q_rot.dtype == qa.dtype,
@@ -1351,10 +1369,10 @@ def latent_attention_wide(qa: torch.Tensor, q_rot: torch.Tensor, c_cache: torch.
     out = torch.empty((T, H, rank), dtype=qa.dtype, device=qa.device)
     f = _fn("attention_latent", "lb_latent_attention_wide", [c_void_p, c_long, c_long, c_void_p, c_long, c_long, c_void_p, c_void_p,
                                                              c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
-                                                             c_int, c_int, c_int, c_float, c_int, c_int, c_void_p])
+                                                             c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p])
     _check(f(_ptr(qa), qa.stride(0), qa.stride(1), _ptr(q_rot), q_rot.stride(0), q_rot.stride(1), _ptr(c_cache), _ptr(kr_cache),
              _ptr(block_table), block_table.shape[1], _ptr(token_req), _ptr(positions), _ptr(blocks), blocks.shape[0], _ptr(out),
-             H, rank, rot, c_cache.shape[1], scale, window, rows, _stream()), "latent_attention_wide", f"(rank {rank}, rot {rot}, rows {rows})")
+             H, rank, rot, c_cache.shape[1], scale, window, rows, _ptr(sinks), _stream()), "latent_attention_wide", f"(rank {rank}, rot {rot}, rows {rows})")
     return out
 
 
@@ -1629,6 +1647,48 @@ def normed_prepare(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_di
     return q
 
 
+def rownorm_prepare(qk: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, positions: torch.Tensor,
+                    slot_mapping: torch.Tensor, table: torch.Tensor, q_weight: torch.Tensor, k_weight: torch.Tensor, eps: float,
+                    k_cache: torch.Tensor, v_cache: torch.Tensor, write_kv: bool = True) -> torch.Tensor:
+    """Queries [tokens, heads, head_dim] from qk = [tokens, q | k]: q and k are each RMS-normed over their WHOLE row (all
+    heads at once) with a weight per column of the row (`q_weight` [heads*head_dim], `k_weight` [kv_heads*head_dim]), then
+    rotated over neighbouring pairs of every head's first `table.shape[1]` columns (table: float32 [positions, n], cos | sin
+    of n/2 pairs; n = 0: no rotation).  The normed, rotated keys go to `k_cache` at the tokens' slots, the keys as they
+    came in go to `v_cache` (the values of this attention are its un-normed keys).  Norms and rotation are 32-bit."""
+    _cuda(qk, positions, slot_mapping, table, q_weight, k_weight, k_cache, v_cache)
+    _i32(positions, "positions"); _i32(slot_mapping, "slot_mapping")
+    T = qk.shape[0]
+    nq, nk = num_heads * head_dim, num_kv_heads * head_dim
+    _need(qk.dim() == 2 and qk.stride(1) == 1 and qk.shape[1] == nq + nk, "qk must be [tokens, q | k] with unit column stride")
+    _need(k_cache.dtype == v_cache.dtype == qk.dtype and k_cache.is_contiguous() and v_cache.is_contiguous()
+          and k_cache.shape[2:] == (num_kv_heads, head_dim) and v_cache.shape[2:] == (num_kv_heads, head_dim),
+          "caches must be [pages, page, kv_heads, head_dim], keys and values alike")
+    _need(q_weight.dtype == torch.float32 and q_weight.shape == (nq,) and q_weight.is_contiguous() and k_weight.dtype == torch.float32
+          and k_weight.shape == (nk,) and k_weight.is_contiguous(), "norm weights must be float32 over the whole q and k rows")
+    _need(table.dtype == torch.float32 and table.dim() == 2 and table.is_contiguous(), "the rotation table must be contiguous float32")
+    q = torch.empty((T, num_heads, head_dim), dtype=qk.dtype, device=qk.device)
+    f = _fn("attention_pooled", "lb_rownorm_prepare", [c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
+                                                       c_float, c_void_p, c_void_p, c_void_p] + [c_int] * 6 + [c_void_p])
+    _check(f(_ptr(qk), qk.stride(0) if T > 1 else qk.shape[1], _ptr(positions), _ptr(slot_mapping), _ptr(table), table.shape[1],
+             max(table.shape[0], 1), _ptr(q_weight), _ptr(k_weight), eps, _ptr(q), _ptr(k_cache), _ptr(v_cache), T, num_heads,
+             num_kv_heads, head_dim, int(write_kv), _code(qk), _stream()), "rownorm_prepare")
+    return q
+
+
+def head_gate(o: torch.Tensor, gate: torch.Tensor, num_heads: int) -> torch.Tensor:
+    """o [tokens, heads * width] (contiguous) times sigmoid(gate[t, h]) per token and head, in place.  gate: [tokens, heads]
+    logits in float32 or o's dtype (a column view is fine)."""
+    _cuda(o, gate)
+    T = o.shape[0]
+    _need(o.dim() == 2 and o.is_contiguous() and o.shape[1] % num_heads == 0, "o must be contiguous [tokens, heads * width]")
+    _need(gate.shape == (T, num_heads) and gate.stride(1) == 1 and gate.dtype in (torch.float32, o.dtype),
+          "gate must be [tokens, heads] in float32 or the activation dtype")
+    f = _fn("attention_pooled", "lb_head_gate", [c_void_p, c_void_p, c_long, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(o), _ptr(gate), gate.stride(0) if T > 1 else max(gate.stride(0), num_heads), int(gate.dtype == torch.float32), T,
+             num_heads, o.shape[1] // num_heads, _code(o), _stream()), "head_gate")
+    return o
+
+
 def pooled_blocks(k_cache: torch.Tensor, v_cache: torch.Tensor, kp_cache: torch.Tensor, vp_cache: torch.Tensor,
                   positions: torch.Tensor, token_req: torch.Tensor, block_table: torch.Tensor, pooled_slots: torch.Tensor,
                   pool: int) -> None:
@@ -1791,20 +1851,22 @@ def pooled_attention_split(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torc
 def delta_scan(qkv: torch.Tensor, z: torch.Tensor, dt_bias: torch.Tensor, A_log: torch.Tensor, beta: torch.Tensor, state: torch.Tensor,
                cu_seqlens: torch.Tensor, start_pos: torch.Tensor, slots: torch.Tensor, num_requests: int, num_heads: int,
                num_key_heads: int, key_dim: int, value_dim: int, q_scale: float, unit_eps: float,
-               request_list: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+               request_list: torch.Tensor | None = None, out: torch.Tensor | None = None, head_decay: bool = False) -> torch.Tensor:
     """Token-by-token gated delta rule per head over every request's tokens (see `csrc/delta.cu`): queries and keys made unit
     vectors (the query times `q_scale`), a decay exp(-exp(A_log) softplus(z + dt_bias)) per key channel, a write gated by
     sigmoid(beta), read-out after the write.  qkv: [tokens, >= 2*Hk*key_dim + H*value_dim] with columns q | k | v first
     (unit column stride; query/key head of value head h is h // (H / Hk)); z: float32 [tokens, H*key_dim]; dt_bias: float32
     [H*key_dim]; A_log: float32 [H]; beta: [tokens, H] logits (float32 or qkv's dtype, a column view allowed); state: float32
-    [slots, H, key_dim, value_dim], updated in place.  Returns float32 [tokens, H*value_dim]."""
+    [slots, H, key_dim, value_dim], updated in place.  Returns float32 [tokens, H*value_dim].  `head_decay`: one decay per
+    head instead of one per key channel: z is float32 [tokens, H] and dt_bias float32 [H]."""
     _cuda(qkv, z, dt_bias, A_log, beta, state, cu_seqlens, start_pos, slots, request_list)
     H, Hk, dk, dv = num_heads, num_key_heads, key_dim, value_dim
     T = qkv.shape[0]
     _need(qkv.dim() == 2 and qkv.stride(1) == 1 and qkv.shape[1] >= 2 * Hk * dk + H * dv, "qkv must hold the columns q | k | v")
-    _need(z.dtype == torch.float32 and z.shape == (T, H * dk) and z.is_contiguous(), "z must be contiguous float32 [tokens, H*key_dim]")
-    _need(dt_bias.dtype == torch.float32 and dt_bias.numel() == H * dk and dt_bias.is_contiguous() and A_log.dtype == torch.float32
-          and A_log.shape == (H,) and A_log.is_contiguous(), "dt_bias float32 [H*key_dim], A_log float32 [H]")
+    zdim = 1 if head_decay else dk
+    _need(z.dtype == torch.float32 and z.shape == (T, H * zdim) and z.is_contiguous(), "z must be contiguous float32 [tokens, H*key_dim] (head_decay: [tokens, H])")
+    _need(dt_bias.dtype == torch.float32 and dt_bias.numel() == H * zdim and dt_bias.is_contiguous() and A_log.dtype == torch.float32
+          and A_log.shape == (H,) and A_log.is_contiguous(), "dt_bias float32 [H*key_dim] (head_decay: [H]), A_log float32 [H]")
     _need(beta.dim() == 2 and beta.shape == (T, H) and beta.stride(1) == 1 and beta.dtype in (torch.float32, qkv.dtype),
           "beta must be [tokens, H] in float32 or the activation dtype")
     _need(state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (H, dk, dv),
@@ -1820,10 +1882,10 @@ def delta_scan(qkv: torch.Tensor, z: torch.Tensor, dt_bias: torch.Tensor, A_log:
     stride = qkv.stride(0) if T > 1 else qkv.shape[1]
     f = _fn("delta", "lb_delta_scan", [c_void_p, c_void_p, c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_int,
                                        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                                       c_float, c_float, c_int, c_void_p])
+                                       c_float, c_float, c_int, c_int, c_void_p])
     _check(f(base, base + Hk * dk * item, base + 2 * Hk * dk * item, stride, _ptr(z), _ptr(dt_bias), _ptr(A_log), _ptr(beta),
              beta.stride(0) if T > 1 else max(beta.stride(0), H), int(beta.dtype == torch.float32), _ptr(o), _ptr(state),
-             _ptr(cu_seqlens), _ptr(start_pos), _ptr(slots), _ptr(request_list), n, H, Hk, dk, dv, q_scale, unit_eps, _code(qkv),
+             _ptr(cu_seqlens), _ptr(start_pos), _ptr(slots), _ptr(request_list), n, H, Hk, dk, dv, q_scale, unit_eps, zdim, _code(qkv),
              _stream()), "delta_scan", f"(key_dim {dk}, value_dim {dv})")
     return o
 
@@ -1839,7 +1901,8 @@ def delta_scan_rows_ok(key_dim: int) -> bool:
 def delta_scan_rows(qkv: torch.Tensor, z: torch.Tensor, dt_bias: torch.Tensor, A_log: torch.Tensor, beta: torch.Tensor, state: torch.Tensor,
                     cu_seqlens: torch.Tensor, start_pos: torch.Tensor, slots: torch.Tensor, num_requests: int, num_heads: int,
                     num_key_heads: int, key_dim: int, value_dim: int, q_scale: float, unit_eps: float,
-                    request_list: torch.Tensor | None = None, out: torch.Tensor | None = None, rows_per_thread: int = 0) -> torch.Tensor:
+                    request_list: torch.Tensor | None = None, out: torch.Tensor | None = None, rows_per_thread: int = 0,
+                    head_decay: bool = False) -> torch.Tensor:
     """`delta_scan` for portions of many tokens: one launch turns every token's unit vectors, decays and gates into 32-bit
     rows, a second one runs the recurrence of the requests of `request_list` (all, if None) with nothing but the state's
     update in its loop.  Operands and result as `delta_scan`; rows of `out` that belong to other requests are left alone."""
@@ -1848,9 +1911,10 @@ def delta_scan_rows(qkv: torch.Tensor, z: torch.Tensor, dt_bias: torch.Tensor, A
     T = qkv.shape[0]
     _need(delta_scan_rows_ok(dk), "delta_scan_rows takes up to 512 key channels")
     _need(qkv.dim() == 2 and qkv.stride(1) == 1 and qkv.shape[1] >= 2 * Hk * dk + H * dv, "qkv must hold the columns q | k | v")
-    _need(z.dtype == torch.float32 and z.shape == (T, H * dk) and z.is_contiguous(), "z must be contiguous float32 [tokens, H*key_dim]")
-    _need(dt_bias.dtype == torch.float32 and dt_bias.numel() == H * dk and dt_bias.is_contiguous() and A_log.dtype == torch.float32
-          and A_log.shape == (H,) and A_log.is_contiguous(), "dt_bias float32 [H*key_dim], A_log float32 [H]")
+    zdim = 1 if head_decay else dk
+    _need(z.dtype == torch.float32 and z.shape == (T, H * zdim) and z.is_contiguous(), "z must be contiguous float32 [tokens, H*key_dim] (head_decay: [tokens, H])")
+    _need(dt_bias.dtype == torch.float32 and dt_bias.numel() == H * zdim and dt_bias.is_contiguous() and A_log.dtype == torch.float32
+          and A_log.shape == (H,) and A_log.is_contiguous(), "dt_bias float32 [H*key_dim] (head_decay: [H]), A_log float32 [H]")
     _need(beta.dim() == 2 and beta.shape == (T, H) and beta.stride(1) == 1 and beta.dtype in (torch.float32, qkv.dtype),
           "beta must be [tokens, H] in float32 or the activation dtype")
     _need(state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (H, dk, dv),
@@ -1872,11 +1936,11 @@ def delta_scan_rows(qkv: torch.Tensor, z: torch.Tensor, dt_bias: torch.Tensor, A
     stride = qkv.stride(0) if T > 1 else qkv.shape[1]
     f = _fn("delta", "lb_delta_scan_rows", [c_void_p, c_void_p, c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_int,
                                             c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_long,
-                                            c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_int, c_void_p])
+                                            c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_int, c_int, c_void_p])
     _check(f(base, base + Hk * dk * item, base + 2 * Hk * dk * item, stride, _ptr(z), _ptr(dt_bias), _ptr(A_log), _ptr(beta),
              beta.stride(0) if T > 1 else max(beta.stride(0), H), int(beta.dtype == torch.float32), _ptr(prepared), _ptr(values),
              _ptr(o), _ptr(state), _ptr(cu_seqlens), _ptr(start_pos), _ptr(slots), _ptr(request_list), n, T, H, Hk, dk, dv, q_scale,
-             unit_eps, rows_per_thread, _code(qkv), _stream()), "delta_scan_rows", f"(key_dim {dk}, value_dim {dv})", launches=2)
+             unit_eps, rows_per_thread, zdim, _code(qkv), _stream()), "delta_scan_rows", f"(key_dim {dk}, value_dim {dv})", launches=2)
     return o
 
 
@@ -1891,7 +1955,8 @@ def delta_scan_chunks_ok(key_dim: int) -> bool:
 def delta_scan_chunks(qkv: torch.Tensor, z: torch.Tensor, dt_bias: torch.Tensor, A_log: torch.Tensor, beta: torch.Tensor, state: torch.Tensor,
                       cu_seqlens: torch.Tensor, start_pos: torch.Tensor, slots: torch.Tensor, chunks: torch.Tensor, num_chunks: int,
                       per_request: torch.Tensor, num_long: int, num_heads: int, num_key_heads: int, key_dim: int, value_dim: int,
-                      q_scale: float, unit_eps: float, out: torch.Tensor | None = None, rows_per_thread: int = 0) -> torch.Tensor:
+                      q_scale: float, unit_eps: float, out: torch.Tensor | None = None, rows_per_thread: int = 0,
+                      head_decay: bool = False) -> torch.Tensor:
     """`delta_scan` for the long portions of a step in chunks of `DELTA_CHUNK` tokens: one launch turns every chunk into a
     32-bit record (unit vectors times the chunk's running decays, the two small triangular matrices between its tokens), a
     second one walks each listed request's chunks with one reduction round per chunk (the 16 sums of a chunk reduced by
@@ -1903,9 +1968,10 @@ def delta_scan_chunks(qkv: torch.Tensor, z: torch.Tensor, dt_bias: torch.Tensor,
     T = qkv.shape[0]
     _need(delta_scan_chunks_ok(dk), "delta_scan_chunks takes up to 256 key channels")
     _need(qkv.dim() == 2 and qkv.stride(1) == 1 and qkv.shape[1] >= 2 * Hk * dk + H * dv, "qkv must hold the columns q | k | v")
-    _need(z.dtype == torch.float32 and z.shape == (T, H * dk) and z.is_contiguous(), "z must be contiguous float32 [tokens, H*key_dim]")
-    _need(dt_bias.dtype == torch.float32 and dt_bias.numel() == H * dk and dt_bias.is_contiguous() and A_log.dtype == torch.float32
-          and A_log.shape == (H,) and A_log.is_contiguous(), "dt_bias float32 [H*key_dim], A_log float32 [H]")
+    zdim = 1 if head_decay else dk
+    _need(z.dtype == torch.float32 and z.shape == (T, H * zdim) and z.is_contiguous(), "z must be contiguous float32 [tokens, H*key_dim] (head_decay: [tokens, H])")
+    _need(dt_bias.dtype == torch.float32 and dt_bias.numel() == H * zdim and dt_bias.is_contiguous() and A_log.dtype == torch.float32
+          and A_log.shape == (H,) and A_log.is_contiguous(), "dt_bias float32 [H*key_dim] (head_decay: [H]), A_log float32 [H]")
     _need(beta.dim() == 2 and beta.shape == (T, H) and beta.stride(1) == 1 and beta.dtype in (torch.float32, qkv.dtype),
           "beta must be [tokens, H] in float32 or the activation dtype")
     _need(state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (H, dk, dv),
@@ -1925,11 +1991,11 @@ def delta_scan_chunks(qkv: torch.Tensor, z: torch.Tensor, dt_bias: torch.Tensor,
     stride = qkv.stride(0) if T > 1 else qkv.shape[1]
     f = _fn("delta", "lb_delta_scan_chunks", [c_void_p, c_void_p, c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_int,
                                               c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
-                                              c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_int, c_void_p])
+                                              c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_int, c_int, c_void_p])
     _check(f(base, base + Hk * dk * item, base + 2 * Hk * dk * item, stride, _ptr(z), _ptr(dt_bias), _ptr(A_log), _ptr(beta),
              beta.stride(0) if T > 1 else max(beta.stride(0), H), int(beta.dtype == torch.float32), _ptr(records), _ptr(values),
              _ptr(o), _ptr(state), _ptr(cu_seqlens), _ptr(start_pos), _ptr(slots), _ptr(chunks), num_chunks, _ptr(per_request), num_long,
-             H, Hk, dk, dv, q_scale, unit_eps, rows_per_thread, _code(qkv), _stream()), "delta_scan_chunks", f"(key_dim {dk}, value_dim {dv})", launches=2)
+             H, Hk, dk, dv, q_scale, unit_eps, rows_per_thread, zdim, _code(qkv), _stream()), "delta_scan_chunks", f"(key_dim {dk}, value_dim {dv})", launches=2)
     return o
 
 

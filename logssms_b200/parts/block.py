@@ -202,6 +202,68 @@ class PostNormBlock(Part):
         return x, None
 
 
+@BLOCKS.register("outnorm_stream")
+class OutNormStreamBlock(Part):
+    """x <- x + norm1(mixer(x)); then, with a feed-forward, x <- x + norm2(ff(x)): the norms sit on the sublayers' outputs
+    alone, and the sublayers read the stream itself.
+
+    The stream x is 32-bit whatever the activation dtype (`K.StreamRows`); the sublayers read its copy rounded to the
+    activation dtype.  One kernel besides the sublayers' own per sublayer: the output's root mean square, the norm's weight, the
+    sum into the stream (all 32-bit) and the rounded copy that the next sublayer reads (`K.stream_add_norm` with `unit_eps`)."""
+    input_norm = None            # no norm reads this block's input: it is handed the stream as it is
+    kernels = ("stream_layer",)
+
+    def __init__(self, spec, perturb_init: bool = False, shared: dict | None = None):
+        self.spec = spec
+        m = spec.mixer
+        if m.in_scale != 1.0 or m.out_scale != 1.0:
+            raise ValueError("outnorm_stream blocks take a mixer without input or output scales")
+        self.mixer = MIXERS.get(m.spec.kind)(m.spec, perturb_init=perturb_init, shared=shared)
+        self.mixer_norm = NORMS.get(spec.mixer_norm.kind)(spec.mixer_norm, perturb_init)
+        self.feed_forward = self.ff_norm = None
+        if spec.feed_forward is not None:
+            self.feed_forward = FEED_FORWARDS.get(spec.feed_forward.kind)(spec.feed_forward, perturb_init=perturb_init,
+                                                                          shared=shared)
+            self.ff_norm = NORMS.get(spec.feed_forward_norm.kind)(spec.feed_forward_norm, perturb_init)
+        for norm in (self.mixer_norm, self.ff_norm):
+            if norm is not None and getattr(norm, "norm_kind", None) != "rmsnorm":
+                raise ValueError("outnorm_stream blocks norm their sublayers' outputs by root mean square (`rmsnorm`)")
+
+    def children(self):
+        s = self.spec
+        kids = {s.mixer_norm_name: self.mixer_norm, s.mixer.name: self.mixer}
+        if self.feed_forward is not None:
+            kids[s.feed_forward_norm_name] = self.ff_norm
+            kids[s.feed_forward_name] = self.feed_forward
+        return kids
+
+    def cache_needs(self):
+        return self.mixer.cache_needs()
+
+    def setup(self, rt) -> None:
+        self.mixer.setup(rt)
+        if self.feed_forward is not None:
+            self.feed_forward.setup(rt)
+
+    def forward(self, x, residual, ctx, cache_layer: int, writes_cache: bool = True):
+        if not isinstance(x, K.StreamRows) or residual is not None:
+            raise ValueError("an outnorm_stream block takes a 32-bit stream (`StreamRows`), as its embedding or the block before leaves it")
+        act = x.act.dtype
+        stream, h = x.f32, x.act
+        if h.shape != stream.shape:                    # the block before left no rounded copy
+            _, h = K.stream_add_norm(stream, None, None, None, 0.0, "none", act)
+        with nvtx_range(self.spec.mixer.spec.kind):
+            y = self.mixer.forward(h, ctx, cache_layer, writes_cache)
+        n = self.mixer_norm
+        _, h = K.stream_add_norm(stream, y, n.weight, None, 0.0, "none", act, unit_eps=n.eps)
+        if self.feed_forward is not None:
+            with nvtx_range(self.spec.feed_forward.kind):
+                y = self.feed_forward.forward(h)
+            n = self.ff_norm
+            _, h = K.stream_add_norm(stream, y, n.weight, None, 0.0, "none", act, unit_eps=n.eps)
+        return K.StreamRows(stream, h), None
+
+
 class SharedTable(Part):
     """A table stored once at the model's root that several layers read (each a slice of every row)."""
 

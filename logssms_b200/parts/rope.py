@@ -50,13 +50,47 @@ class RotaryEmbedding(Part):
         self.spec = spec
         self.table: torch.Tensor | None = None
 
+    def frequencies(self) -> tuple[torch.Tensor, float]:
+        """(float32 frequency per pair, the factor on every cos and sin)."""
+        return inverse_frequencies(self.spec), 1.0
+
     def setup(self, rt) -> None:
         # one row per position the engine can ever hold: its sequence limit replaces the model's
         # max_position_embeddings when the two differ (python/logssms/engine/config.py:76-80), and the kernels
         # index the table by position without a check of their own
         rows = max(rt.max_seq_len, 1)
         if self.table is None or self.table.shape[0] != rows or self.table.device != rt.device:
-            self.table = K.rope_table(inverse_frequencies(self.spec).to(rt.device), rows)
+            inv, magnitude = self.frequencies()
+            self.table = K.rope_table(inv.to(rt.device), rows, magnitude)
+
+
+def ramp_frequencies(rotary_dim: int, theta: float, scaling) -> tuple[torch.Tensor, float]:
+    """Frequencies f_i = theta^(-2i/n) of the n/2 pairs, stretched by a ramp over the pair index: with `scaling` (factor,
+    original, fast, slow) and dim(t) = n ln(original / (2 pi t)) / (2 ln theta), lo = max(floor(dim(fast)), 0), hi =
+    min(ceil(dim(slow)), n - 1), ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), the frequency is f_i / factor * ramp_i +
+    f_i (1 - ramp_i), and every cos and sin is multiplied by 0.1 ln(factor) + 1.  Worked out in float64, handed on as float32."""
+    n = rotary_dim
+    f = torch.tensor([theta ** (-2.0 * i / n) for i in range(n // 2)], dtype=torch.float64)
+    if not scaling:
+        return f.to(torch.float32), 1.0
+    sc = dict(scaling)
+    factor, original = float(sc["factor"]), float(sc["original"])
+
+    def dim_of(turns: float) -> float:
+        return n * math.log(original / (2 * math.pi * turns)) / (2 * math.log(theta))
+    lo = max(math.floor(dim_of(float(sc["fast"]))), 0)
+    hi = min(math.ceil(dim_of(float(sc["slow"]))), n - 1)
+    ramp = torch.clamp((torch.arange(n // 2, dtype=torch.float64) - lo) / max(hi - lo, 0.001), 0, 1)
+    return (f / factor * ramp + f * (1 - ramp)).to(torch.float32), 0.1 * math.log(factor) + 1.0
+
+
+@POSITION_ENCODINGS.register("rope_ramp")
+class RampRotaryEmbedding(RotaryEmbedding):
+    """The same table with the frequencies and the factor of `ramp_frequencies` (`spec.scaling`: the items factor, original,
+    fast, slow; None: plain frequencies).  Which columns form a pair is the reading kernel's business."""
+
+    def frequencies(self) -> tuple[torch.Tensor, float]:
+        return ramp_frequencies(self.spec.rotary_dim, self.spec.theta, self.spec.scaling)
 
 
 class NoPositionEncoding(Part):
