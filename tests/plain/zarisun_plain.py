@@ -2,7 +2,8 @@
 token by token where the design is a recurrence.  It shares no code with the engine; the engine's tests compare against it.
 
 A model is (config mapping, {tensor name: tensor}); a request is a list of token ids.  `forward` returns the logits at
-every position and, on request, the stream after every layer.
+every position and, on request, the stream after every layer.  With another `dtype` than float64 every tensor and every
+intermediate result is of that dtype (angles excepted): what rounding alone does to a model.
 """
 from __future__ import annotations
 
@@ -46,11 +47,14 @@ def yarn_frequencies(rot):
 
 
 def rotate(x, positions, rot):
-    """x [T, heads, d]: neighbouring pairs of the first rot.dims columns of every head turn by position * frequency."""
+    """x [T, heads, d]: neighbouring pairs of the first rot.dims columns of every head turn by position * frequency
+    (`rot` None: nothing turns)."""
+    if rot is None:
+        return x
     dims = int(rot["dims"])
     f, m = yarn_frequencies(rot)
     a = positions.to(F)[:, None] * f[None, :]
-    cos, sin = (torch.cos(a) * m)[:, None, :], (torch.sin(a) * m)[:, None, :]
+    cos, sin = (torch.cos(a) * m)[:, None, :].to(x.dtype), (torch.sin(a) * m)[:, None, :].to(x.dtype)
     u, v = x[..., 0:dims:2], x[..., 1:dims:2]
     out = x.clone()
     out[..., 0:dims:2] = u * cos - v * sin
@@ -62,7 +66,7 @@ def sink_softmax_attention(q, k, v, scale, sink, window):
     """q [T, H, d], k [T, H, d], v [T, H, dv] (keys already repeated per query head); position i sees j with
     0 <= i - j < window (None: every j <= i); the denominator also holds exp(sink_h)."""
     T, H = q.shape[0], q.shape[1]
-    out = torch.zeros(T, H, v.shape[-1], dtype=F)
+    out = torch.zeros(T, H, v.shape[-1], dtype=q.dtype)
     for i in range(T):
         lo = 0 if window is None else max(0, i - window + 1)
         for h in range(H):
@@ -83,10 +87,10 @@ def conv_attention(h, p, m, eps):
     q = rms_norm(q, p["q.norm"], eps).view(T, H, d)
     k = rms_norm(k, p["k.norm"], eps).view(T, G, d)
     pos = torch.arange(T)
-    q, k = rotate(q, pos, m["rot"]), rotate(k, pos, m["rot"])
+    q, k = rotate(q, pos, m.get("rot")), rotate(k, pos, m.get("rot"))
     rep = H // G
     o = sink_softmax_attention(q, k.repeat_interleave(rep, 1), v.repeat_interleave(rep, 1), float(m["scale"]), p["sink"],
-                               int(m["mask"]["size"]))
+                               None if m.get("mask") is None else int(m["mask"]["size"]))
     o = o * torch.sigmoid(h @ p["g"].T)[:, :, None]
     return o.reshape(T, -1) @ p["o"].T
 
@@ -96,7 +100,7 @@ def latent_kv(h, p, m, eps):
     T, rank = h.shape[0], int(m["kv_rank"])
     d = h @ p["dkv"].T
     c = rms_norm(d[:, :rank], p["dkv.norm"], eps)
-    kr = rotate(d[:, None, rank:], torch.arange(T), m["rot"])[:, 0]
+    kr = rotate(d[:, None, rank:], torch.arange(T), m.get("rot"))[:, 0]
     return c, kr
 
 
@@ -104,7 +108,7 @@ def latent_attention(h, p, m, eps, c, kr):
     T = h.shape[0]
     H, d, r, dv = int(m["heads"]), int(m["dim"]), int(m["rot_dim"]), int(m["vdim"])
     q = (h @ p["q"].T).view(T, H, d + r)
-    q_rot = rotate(q[..., d:], torch.arange(T), m["rot"])
+    q_rot = rotate(q[..., d:], torch.arange(T), m.get("rot"))
     k_nope = (c @ p["uk"].T).view(T, H, d)
     v = (c @ p["uv"].T).view(T, H, dv)
     qq = torch.cat([q[..., :d], q_rot], -1)
@@ -126,8 +130,8 @@ def delta_rule(h, p, m, eps):
     beta = torch.sigmoid(h @ p["b"].T)
     g = torch.exp(-torch.exp(p["A_log"]) * torch.nn.functional.softplus(h @ p["a"].T + p["dt_bias"]))
     gate = silu(h @ p["g"].T).view(T, H, dv)
-    o = torch.zeros(T, H, dv, dtype=F)
-    S = torch.zeros(H, dk, dv, dtype=F)
+    o = torch.zeros(T, H, dv, dtype=h.dtype)
+    S = torch.zeros(H, dk, dv, dtype=h.dtype)
     for t in range(T):
         for j in range(H):
             kj, qj = k[t, j // (H // G)], q[t, j // (H // G)]
@@ -143,19 +147,19 @@ def dense_ff(h, p):
     return (torch.nn.functional.silu(h @ p["gate"].T) * (h @ p["up"].T)) @ p["down"].T
 
 
-def layer_tensors(tensors, prefix):
-    return {k[len(prefix):]: v.to(F) for k, v in tensors.items() if k.startswith(prefix)}
+def layer_tensors(tensors, prefix, dtype=F):
+    return {k[len(prefix):]: v.to(dtype) for k, v in tensors.items() if k.startswith(prefix)}
 
 
-def forward(config, tensors, tokens, want_layers=False):
+def forward(config, tensors, tokens, want_layers=False, dtype=F):
     """Logits [T, vocab] of one sequence (and the stream after every layer, [layers, T, width])."""
     eps = float(config["norm"]["eps"])
-    embed = tensors["embed"].to(F)
+    embed = tensors["embed"].to(dtype)
     x = embed[torch.tensor(tokens)]
     streams, latents = [], {}
     for i, layer in enumerate(config["layers"]):
         m = layer["mixer"]
-        p = layer_tensors(tensors, f"l{i}.mix.")
+        p = layer_tensors(tensors, f"l{i}.mix.", dtype)
         if layer["type"] == "attention":
             y = conv_attention(x, p, m, eps)
         elif layer["type"] == "delta":
@@ -167,12 +171,12 @@ def forward(config, tensors, tokens, want_layers=False):
             y = latent_attention(x, p, m, eps, *latents[i if src is None else int(src)])
         else:
             raise ValueError(layer["type"])
-        x = x + rms_norm(y, tensors[f"l{i}.norm1"].to(F), eps)
+        x = x + rms_norm(y, tensors[f"l{i}.norm1"].to(dtype), eps)
         if layer.get("mlp") is not None:
-            y = dense_ff(x, layer_tensors(tensors, f"l{i}.mlp."))
-            x = x + rms_norm(y, tensors[f"l{i}.norm2"].to(F), eps)
+            y = dense_ff(x, layer_tensors(tensors, f"l{i}.mlp.", dtype))
+            x = x + rms_norm(y, tensors[f"l{i}.norm2"].to(dtype), eps)
         streams.append(x)
-    logits = rms_norm(x, tensors["final.norm"].to(F), eps) @ embed.T * float(config["logit_scale"])
+    logits = rms_norm(x, tensors["final.norm"].to(dtype), eps) @ embed.T * float(config["logit_scale"])
     if want_layers:
         return logits, torch.stack(streams)
     return logits

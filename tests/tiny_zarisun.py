@@ -168,10 +168,10 @@ def read_folder(model_dir: str):
     return config, load_file(os.path.join(model_dir, "model.safetensors"))
 
 
-def plain_logits(model_dir: str, ids) -> torch.Tensor:
-    """The plain model's float64 logits at every position, from the folder's stored weights."""
+def plain_logits(model_dir: str, ids, dtype=torch.float64) -> torch.Tensor:
+    """The plain model's logits at every position, from the folder's stored weights (in `dtype` throughout)."""
     config, tensors = read_folder(model_dir)
-    return P.forward(config, tensors, list(ids))
+    return P.forward(config, tensors, list(ids), dtype=dtype).double()
 
 
 def row_errors(got: torch.Tensor, want: torch.Tensor) -> torch.Tensor:
@@ -185,4 +185,4 @@ def row_errors(got: torch.Tensor, want: torch.Tensor) -> torch.Tensor:
     return d.pow(2).mean(-1).sqrt() / want.pow(2).mean(-1).sqrt().clamp_min(1e-30)
 
 
-TOL = {"float32": 2e-4, "bfloat16": 5e-2}
+TOL = {"float32": 3e-4, "bfloat16": 5e-2}
