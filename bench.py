@@ -813,7 +813,35 @@ PUPOPEL_SIZES = {
     "w1024": (_pupopel_config(1024, 4, 8, 2, 64, 128, 8, 2, 1024, 1024, 2048, 32768), DESIGN_SIZES["w1024"][0]),
     "w2048": (_pupopel_config(2048, 4, 16, 4, 128, 128, 16, 4, 1408, 1408, 8192, 65536), DESIGN_SIZES["w2048"][0]),
 }
-DESIGNS = {"dudurax": (DESIGN_SIZES, "falcon_h1"), "kuvazen": (KUVAZEN_SIZES, "dudurax"), "pupopel": (PUPOPEL_SIZES, "dudurax")}
+
+
+def _zarisun_config(width: int, heads: int, kv_heads: int, key_dim: int, value_dim: int, kv_rank: int, rot: int, window: int,
+                    dense_ff: int, vocab: int) -> dict:
+    """Layer sizes that resemble a real model's, every mixer once and a reader of another layer's latents: a gated delta rule
+    with one decay per head, attention over a window whose values are its convolved keys, attention over cached latents, and
+    a second one that reads the first one's cache; dense feed-forwards."""
+    scaling = {"factor": 8.0, "original": 2048, "fast": 32.0, "slow": 1.0}
+    delta = {"type": "delta", "mixer": {"heads": heads, "kv_heads": heads, "dim": key_dim, "vdim": value_dim, "conv": 4}}
+    attention = {"type": "attention",
+                 "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": key_dim, "vdim": key_dim, "conv": 4, "mask": {"size": window},
+                           "rot": {"base": 10000.0, "dims": key_dim // 2, "scaling": scaling}, "scale": key_dim ** -0.5}}
+    latent = {"heads": heads, "dim": key_dim, "rot_dim": rot, "vdim": key_dim, "kv_rank": kv_rank,
+              "rot": {"base": 10000.0, "dims": rot, "scaling": scaling}, "scale": (key_dim + rot) ** -0.5}
+    ff = {"kind": "dense", "ff": dense_ff}
+    layers = [{**delta, "mlp": ff}, {**attention, "mlp": ff}, {"type": "latent_attention", "mixer": latent, "mlp": ff},
+              {"type": "latent_attention", "mixer": {**latent, "kv_from": 2}, "mlp": ff}]
+    return {"architecture": "Zarisun", "layers": layers, "norm": {"eps": 1e-5}, "logit_scale": 1.0, "vocab": vocab, "width": width}
+
+
+# Zarisun beside Pupopel (the closest existing model: a 32-bit stream, a gated delta rule on the same kernels, softmax attention
+# with a sink on the same kernels; its latent attention is Dudurax's, whose numbers stand in the same tables) at the same width,
+# depth, vocabulary and head sizes
+ZARISUN_SIZES = {
+    "w1024": (_zarisun_config(1024, 8, 2, 64, 128, 256, 32, 1024, 2048, 32768), PUPOPEL_SIZES["w1024"][0]),
+    "w2048": (_zarisun_config(2048, 16, 4, 128, 128, 512, 64, 2048, 8192, 65536), PUPOPEL_SIZES["w2048"][0]),
+}
+DESIGNS = {"dudurax": (DESIGN_SIZES, "falcon_h1"), "kuvazen": (KUVAZEN_SIZES, "dudurax"), "pupopel": (PUPOPEL_SIZES, "dudurax"),
+           "zarisun": (ZARISUN_SIZES, "pupopel")}
 
 
 def _design_point(cfg: dict, vocab: int, K: int, W: int, batch: int, context: int) -> dict:
@@ -886,7 +914,7 @@ def _design_point(cfg: dict, vocab: int, K: int, W: int, batch: int, context: in
 
 def run_design(args) -> dict:
     """`--design NAME`: that design at a few layer sizes beside the closest existing model at the same width and depth
-    (Dudurax beside Falcon-H1, Kuvazen and Pupopel beside Dudurax)."""
+    (Dudurax beside Falcon-H1, Kuvazen and Pupopel beside Dudurax, Zarisun beside Pupopel)."""
     table, beside = DESIGNS[args.design]
     sizes = {}
     for name, (new, closest) in table.items():
@@ -947,7 +975,7 @@ def main() -> int:
     ap.add_argument("--reference-timeout", type=int, default=900, help="seconds the reference arm may take")
     ap.add_argument("--probe", choices=["decode", "prefill", "mixed"], default=None,
                     help="a short run of one kind of step for a profiler (see profiles/); prints no benchmark line")
-    ap.add_argument("--design", choices=["dudurax", "kuvazen", "pupopel"], default=None,
+    ap.add_argument("--design", choices=["dudurax", "kuvazen", "pupopel", "zarisun"], default=None,
                     help="prefill and decode of another design at a few layer sizes beside the closest existing model "
                          "(one JSON line of its own; the default workload is untouched)")
     args = ap.parse_args()
