@@ -929,6 +929,49 @@ __global__ void __launch_bounds__(256) rownorm_prepare_kernel(const T* __restric
     }
 }
 
+// The same for bfloat16 rows whose columns come in aligned pairs (an even head size and row stride): a thread owns the pairs
+// (2i, 2i + 1), which are also the rotation's pairs, and moves them as 4-byte words.
+__global__ void __launch_bounds__(256) rownorm_prepare_pairs_kernel(const __nv_bfloat162* __restrict__ qk, long row_pairs,
+                                                                    const int* __restrict__ positions, const int* __restrict__ slot_mapping,
+                                                                    const float* __restrict__ table, int rot, int table_rows,
+                                                                    const float2* __restrict__ wq, const float2* __restrict__ wk, float eps,
+                                                                    __nv_bfloat162* __restrict__ q_out, __nv_bfloat162* __restrict__ k_cache,
+                                                                    __nv_bfloat162* __restrict__ v_cache, int Hq, int Hkv, int dim, int write_kv) {
+    __shared__ float red[32];
+    const size_t t = blockIdx.x;
+    const __nv_bfloat162* row = qk + t * row_pairs;
+    const int pq = Hq * dim / 2, pk = Hkv * dim / 2, pd = dim / 2;
+    float sq = 0.f, sk = 0.f;
+    for (int c = threadIdx.x; c < pq; c += blockDim.x) { const float2 v = __bfloat1622float2(row[c]); sq += v.x * v.x + v.y * v.y; }
+    for (int c = threadIdx.x; c < pk; c += blockDim.x) { const float2 v = __bfloat1622float2(row[pq + c]); sk += v.x * v.x + v.y * v.y; }
+    const float inv_q = 1.f / sqrtf(block_sum(sq, red) / (float)(2 * pq) + eps);
+    const float inv_k = 1.f / sqrtf(block_sum(sk, red) / (float)(2 * pk) + eps);
+    const int pos = min(max(positions[t], 0), table_rows - 1);
+    const float* cs = table + (size_t)pos * rot;
+    const int half = rot >> 1;
+    const long slot = write_kv ? (long)slot_mapping[t] : -1;
+    for (int c = threadIdx.x; c < pq + pk; c += blockDim.x) {
+        const bool is_q = c < pq;
+        const int cc = is_q ? c : c - pq;
+        const int d = cc % pd;                               // pair of its head
+        const __nv_bfloat162 raw = row[c];
+        const float2 v = __bfloat1622float2(raw), w = is_q ? wq[cc] : wk[cc];
+        const float inv = is_q ? inv_q : inv_k;
+        float a = v.x * inv * w.x, b = v.y * inv * w.y;
+        if (d < half) {
+            const float co = cs[d], si = cs[half + d];
+            const float ra = a * co - b * si, rb = b * co + a * si;
+            a = ra; b = rb;
+        }
+        const __nv_bfloat162 out = __floats2bfloat162_rn(a, b);
+        if (is_q) q_out[t * pq + cc] = out;
+        else if (slot >= 0) {
+            k_cache[(size_t)slot * pk + cc] = out;
+            v_cache[(size_t)slot * pk + cc] = raw;
+        }
+    }
+}
+
 // qk: [tokens, (Hq + Hkv) * dim] (column view allowed); table: float32 [table_rows, rot]; wq: float32 [Hq * dim];
 // wk: float32 [Hkv * dim]; q_out: [tokens, Hq, dim]; caches: [slots, Hkv, dim], both
 extern "C" int lb_rownorm_prepare(const void* qk, long row_stride, const int* positions, const int* slot_mapping, const float* table,
@@ -936,6 +979,13 @@ extern "C" int lb_rownorm_prepare(const void* qk, long row_stride, const int* po
                                   void* v_cache, int tokens, int Hq, int Hkv, int dim, int write_kv, int dtype, void* stream) {
     if (tokens <= 0) return kOk;
     if (Hq <= 0 || Hkv <= 0 || dim <= 0 || rot < 0 || rot > dim || (rot & 1) || table_rows <= 0) return kBadSize;
+    if (dtype == kBF16 && dim % 2 == 0 && row_stride % 2 == 0 && ((uintptr_t)qk & 3) == 0 && ((uintptr_t)wq & 7) == 0 && ((uintptr_t)wk & 7) == 0) {
+        typedef __nv_bfloat162 b2;
+        rownorm_prepare_pairs_kernel<<<tokens, 256, 0, (cudaStream_t)stream>>>(
+            (const b2*)qk, row_stride / 2, positions, slot_mapping, table, rot, table_rows, (const float2*)wq, (const float2*)wk, eps,
+            (b2*)q_out, (b2*)k_cache, (b2*)v_cache, Hq, Hkv, dim, write_kv);
+        return launch_status();
+    }
     LB_DISPATCH_DTYPE(dtype, rownorm_prepare_kernel<T><<<tokens, 256, 0, (cudaStream_t)stream>>>(
         (const T*)qk, row_stride, positions, slot_mapping, table, rot, table_rows, wq, wk, eps, (T*)q_out, (T*)k_cache, (T*)v_cache,
         Hq, Hkv, dim, write_kv));
@@ -952,12 +1002,35 @@ __global__ void head_gate_kernel(T* __restrict__ o, const TG* __restrict__ g, lo
     o[i] = from_f32<T>(to_f32(o[i]) * gate);
 }
 
+// bfloat16 rows of a width that is a multiple of 8: a thread scales 8 neighbouring columns of one head (one 16-byte word)
+template <typename TG>
+__global__ void head_gate_vec_kernel(uint4* __restrict__ o, const TG* __restrict__ g, long g_stride, int H, int groups, long total) {
+    const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const long th = i / groups;                             // (token, head)
+    const long t = th / H;
+    const int h = (int)(th % H);
+    const float gate = 1.f / (1.f + expf(-to_f32(g[t * g_stride + h])));
+    uint4 v = o[i];
+    __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) { const float2 f = __bfloat1622float2(p[e]); p[e] = __floats2bfloat162_rn(f.x * gate, f.y * gate); }
+    o[i] = v;
+}
+
 // o: contiguous [tokens, H, width], scaled in place; g: [tokens, >= H] gate logits (float32 with `g_f32`, else o's dtype; row
 // stride in elements)
 extern "C" int lb_head_gate(void* o, const void* g, long g_stride, int g_f32, int tokens, int H, int width, int dtype, void* stream) {
     if (tokens <= 0) return kOk;
     if (H <= 0 || width <= 0) return kBadSize;
     const long total = (long)tokens * H * width;
+    if (dtype == kBF16 && width % 8 == 0 && ((uintptr_t)o & 15) == 0) {
+        const long words = total / 8;
+        const unsigned vblocks = (unsigned)((words + 255) / 256);
+        if (g_f32) head_gate_vec_kernel<float><<<vblocks, 256, 0, (cudaStream_t)stream>>>((uint4*)o, (const float*)g, g_stride, H, width / 8, words);
+        else head_gate_vec_kernel<__nv_bfloat16><<<vblocks, 256, 0, (cudaStream_t)stream>>>((uint4*)o, (const __nv_bfloat16*)g, g_stride, H, width / 8, words);
+        return launch_status();
+    }
     const unsigned blocks = (unsigned)((total + 255) / 256);
     LB_DISPATCH_DTYPE(dtype, {
         if (g_f32) head_gate_kernel<T, float><<<blocks, 256, 0, (cudaStream_t)stream>>>((T*)o, (const float*)g, g_stride, H, width, total);

@@ -292,14 +292,15 @@ def test_block_norms_its_sublayers_outputs(dtype, ff):
         close(y, h, dtype)
 
 
+@pytest.mark.parametrize("width", [12, 16, 1, 64])                 # multiples of 8 take the form of 16-byte words in bfloat16
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_head_gate_kernel(dtype):
+def test_head_gate_kernel(dtype, width):
     from logssms_b200.ops import kernels as K
     g = torch.Generator().manual_seed(0)
-    o = torch.randn(37, 5 * 12, generator=g).to(dtype).cuda()
+    o = torch.randn(37, 5 * width, generator=g).to(dtype).cuda()
     wide = torch.randn(37, 9, generator=g).cuda()
     for gate in (wide[:, 2:7], wide.to(dtype)[:, 2:7]):                        # float32 and activation-dtype logits, column views
-        want = (o.double().view(37, 5, 12) * torch.sigmoid(gate.double())[:, :, None]).view(37, 60)
+        want = (o.double().view(37, 5, width) * torch.sigmoid(gate.double())[:, :, None]).view(37, 5 * width)
         close(K.head_gate(o.clone(), gate, 5), want, dtype)
 
 
