@@ -1002,6 +1002,19 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, *
     return y
 
 
+def linear_f32(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """x [M, K] @ w[N, K]^T as float32 whose sums were never rounded to the activation dtype: what enters a recurrence's
+    32-bit arithmetic (a decay's input).  Few bfloat16 rows: the weight-streaming kernel with its float32 output; more: the
+    library product with float32 output; float32 activations: the engine's own 32-bit kernel."""
+    _cuda(x, w)
+    if x.dtype == torch.float32:
+        return gemm_f32(x, w.float())
+    if w.dtype == torch.bfloat16 and _skinny_ok(x, w, None):
+        return linear_skinny(x, w, out_f32=True)
+    product = lambda: torch.mm(x, w.to(x.dtype).t(), out_dtype=torch.float32)
+    return PROFILER.timed("library", "mm", product) if PROFILER.enabled else product()
+
+
 def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, act_scale: float) -> torch.Tensor:
     """silu(round(gate * act_scale)) * up with [gate | up] = x @ w_gate_up^T (w rows: gate, then up).
     `x` may be `NormedRows`."""

@@ -184,7 +184,7 @@ class GatedDelta(Part):
         C = 2 * Hk * dk + H * dv
         G = H * dv
         proj = K.linear(x, self.in_w)                                     # q | k | v | output gate | write gate
-        z = K.linear(x, self.a_w, out_f32=True)                           # the decay's input, handed on in 32-bit
+        z = K.linear_f32(x, self.a_w)                                     # the decay's input: sums handed on unrounded
         states = ctx.cache.states[cache_layer]
         conv = K.causal_conv1d(proj[:, :C], self.conv_w, None, states["conv"] if s.conv_kernel > 1 else None, ctx.cu_seqlens,
                                ctx.start_pos, ctx.slots, ctx.num_requests, ctx.max_len, (C, C), (1.0, 1.0, 1.0))
