@@ -820,7 +820,7 @@ def _zarisun_config(width: int, heads: int, kv_heads: int, key_dim: int, value_d
     """Layer sizes that resemble a real model's, every mixer once and a reader of another layer's latents: a gated delta rule
     with one decay per head, attention over a window whose values are its convolved keys, attention over cached latents, and
     a second one that reads the first one's cache; dense feed-forwards."""
-    scaling = {"factor": 8.0, "original": 2048, "fast": 32.0, "slow": 1.0}
+    scaling = {"factor": 4.0, "original": 4096, "fast": 16.0, "slow": 1.0}
     delta = {"type": "delta", "mixer": {"heads": heads, "kv_heads": heads, "dim": key_dim, "vdim": value_dim, "conv": 4}}
     attention = {"type": "attention",
                  "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": key_dim, "vdim": key_dim, "conv": 4, "mask": {"size": window},

@@ -64,7 +64,7 @@ def rot(dims, base, scaling=None):
 
 
 # --------------------------------------------------------------------------- the rotation table
-@pytest.mark.parametrize("r", [rot(8, 16.0), rot(8, 16.0, (4.0, 64, 4.0, 1.0)), rot(32, 50000.0, (8.0, 2048, 32.0, 1.0)), rot(2, 7.0, (3.0, 8, 2.0, 1.0))])
+@pytest.mark.parametrize("r", [rot(8, 16.0), rot(8, 16.0, (4.0, 64, 4.0, 1.0)), rot(32, 40000.0, (4.0, 1024, 16.0, 2.0)), rot(2, 7.0, (3.0, 8, 2.0, 1.0))])
 def test_rotation_table(r):
     from logssms_b200.parts.rope import RampRotaryEmbedding
     enc = RampRotaryEmbedding(rope_spec(r["dims"], r))
@@ -93,7 +93,7 @@ def attention_part(dtype, heads, kv_heads, dim, conv, window, r, scale=0.3, seed
 @pytest.mark.parametrize("heads, kv_heads, dim, conv, window, r", [
     (6, 2, 16, 3, 20, rot(8, 500.0, (8.0, 32, 16.0, 2.0))), (4, 1, 32, 2, 70, rot(32, 10000.0)), (2, 2, 16, 1, 1, None),
     (1, 1, 2, 1, 2, rot(2, 100.0)), (4, 2, 8, 4, 64, rot(4, 1000.0)), (2, 1, 24, 5, None, rot(24, 8000.0, (16.0, 128, 32.0, 1.0))),
-    (3, 3, 40, 8, 17, rot(6, 30.0, (2.0, 8, 4.0, 0.5))), (8, 2, 64, 4, 33, rot(16, 20000.0, (8.0, 512, 32.0, 1.0))), (5, 1, 6, 3, 16, rot(6, 9.0))])
+    (3, 3, 40, 8, 17, rot(6, 30.0, (2.0, 8, 4.0, 0.5))), (8, 2, 64, 4, 33, rot(16, 30000.0, (4.0, 256, 16.0, 1.0))), (5, 1, 6, 3, 16, rot(6, 9.0))])
 def test_conv_attention_in_portions(dtype, heads, kv_heads, dim, conv, window, r):
     part, stored, m = attention_part(dtype, heads, kv_heads, dim, conv, window, r, seed=heads + dim)
     # sharp queries: single keys carry the output, so one that is missing or surplus shows
@@ -158,7 +158,7 @@ def latent_part(dtype, heads, dim, rot_dim, vdim, rank, r, own=True, scale=0.25,
 @pytest.mark.parametrize("heads, dim, rot_dim, vdim, rank, r, reader", [
     (3, 24, 16, 8, 32, rot(16, 10000.0, (4.0, 64, 8.0, 1.0)), (2, 8, 24)), (4, 16, 16, 16, 64, rot(16, 30000.0, (2.0, 16, 4.0, 0.5)), (4, 16, 16)),
     (1, 1, 2, 1, 3, rot(2, 50.0), (1, 2, 1)), (3, 5, 6, 7, 11, rot(6, 3000.0, (8.0, 20, 4.0, 1.0)), (5, 3, 9)),
-    (16, 8, 16, 8, 32, rot(8, 100.0), (2, 8, 8)), (5, 8, 32, 24, 96, rot(32, 50000.0, (8.0, 2048, 32.0, 1.0)), (7, 4, 4))])
+    (16, 8, 16, 8, 32, rot(8, 100.0), (2, 8, 8)), (5, 8, 32, 24, 64, rot(32, 40000.0, (4.0, 1024, 16.0, 2.0)), (7, 4, 4))])
 def test_latent_attention_and_a_reader_of_its_cache(dtype, heads, dim, rot_dim, vdim, rank, r, reader):
     if vdim == 1 and dtype == torch.bfloat16:
         pytest.skip("sizes of 1 are covered in float32")

@@ -80,7 +80,7 @@ ZARI_C = _model(48, 130, 1e-5, 1.0, [
 ])
 
 # D: recurrent layers only (no paged cache at all)
-ZARI_D = _model(40, 90, 1e-5, 2.0, [
+ZARI_D = _model(40, 90, 1e-5, 2.5, [
     {**_delta(2, 1, 40, 72, 4), "mlp": _dense(64)},
     {**_delta(4, 4, 16, 16, 3), "mlp": None},
 ])
@@ -110,7 +110,7 @@ def random_zarisun(seed: int) -> dict:
             return None
         dims = 2 * rng.randint(1, limit // 2)
         sc = None if rng.random() < 0.4 else (rng.choice([2.0, 4.0, 8.0, 32.0]), rng.choice([16, 64, 512]), rng.choice([4.0, 32.0]), rng.choice([0.5, 1.0]))
-        return _rot(dims, rng.choice([100.0, 10000.0, 50000.0]), sc)
+        return _rot(dims, rng.choice([100.0, 10000.0, 40000.0]), sc)
     for i in range(rng.randint(2, 6)):
         r = rng.random()
         if r < 0.3:
